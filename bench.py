@@ -1,0 +1,330 @@
+#!/usr/bin/env python
+"""Benchmark of the tensor-parallel attention block (attention + W_o + AllReduce) on N B200s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--mode stream|megatron]
+
+One rank per GPU (torchrun sets RANK / LOCAL_RANK / WORLD_SIZE). A step is one pass of the block over
+the whole sequence. Workload: S=32768, H=32, d_h=128 (d=4096), causal, tile=128, ncomm=4, heads
+sharded over the N ranks (strong scaling: the global problem is fixed). Rank 0 prints one JSON line.
+
+`value` is the block time with the fp16 inputs resident in HBM; `e2e` is the same block through the
+host-buffer entry point (pinned host Q/K/V/W_O copied in, fp16 result copied out, every step).
+`--impl reference` times the unmodified reference programs built under oracle/_ref (its own CUDA
+build; the reference has no CPU implementation), or says why it cannot.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOAD = dict(S=32768, H=32, d_h=128, causal=1, tile=128, ncomm=4, split=1, nbuf=2)
+METRIC = "ms per TP attention block (attn+W_o+AllReduce)"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            pk = json.load(f)
+        return dict(tflops=float(pk["bf16_tflops"]), tflops_sustained=float(pk.get("bf16_tflops_sustained", pk["bf16_tflops"])),
+                    hbm_gbs=float(pk["hbm_gbs"]), source="measured")
+    return dict(tflops=1590.0, tflops_sustained=1400.0, hbm_gbs=6650.0, source="fallback")
+
+
+def attention_flops(S, d_h, H_local, causal):
+    """Algorithmic FLOPs of one rank's attention: 4*S^2*d_h*H_local, or for causal the block-granular
+    count of 64-row blocks sweeping keys 0..(i+1)*64."""
+    if not causal:
+        return 4.0 * S * S * d_h * H_local
+    nb = S // 64
+    return 4.0 * 64 * 64 * d_h * H_local * nb * (nb + 1) / 2
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index):
+        self.device_index = device_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.device_index)],
+                                         stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        out = dict(sm_mhz=None, sm_max_mhz=None, reasons=[], samples=0)
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, reasons, mx = [], set(), None
+        try:
+            for line in open(self.path):
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    sm.append(float(f[1]))
+                    mx = float(f[2])
+                except ValueError:
+                    continue
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except OSError:
+            pass
+        if sm:
+            busy = [x for x in sm if x >= 0.5 * max(sm)] or sm
+            out.update(sm_mhz=statistics.median(busy), sm_max_mhz=mx, reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+def cpu_baseline(pkg, oracle, p, bits_rank0, budget_rows):
+    """The CPU checker (a port: the reference has no CPU path) timed on a bounded sample of query rows of
+    rank 0's shard, scaled to the whole sequence. Rows are spread evenly, so the causal average holds."""
+    import numpy as np
+    vals = tuple(oracle.widen_f16(b) for b in bits_rank0)
+    rows = np.linspace(0, p.S - 1, budget_rows).astype(np.int32)
+    t0 = time.perf_counter()
+    oracle.block_rows([vals], p.d, p.causal, rows)
+    dt = time.perf_counter() - t0
+    threads = int(os.environ.get("OMP_NUM_THREADS", os.cpu_count() or 1))
+    return dict(value=dt * 1e3 * p.S / budget_rows, unit="ms", cores=threads, kind="port",
+                sample=f"{budget_rows} evenly spaced query rows of rank 0's {p.H_local} heads, full key sweep, "
+                       f"{dt:.1f} s measured, scaled by S/rows (extrapolated)")
+
+
+def run_reference(args, world_size, rank):
+    """The unmodified reference (its own attn_bench, built for sm_100a under oracle/_ref with the
+    shared-memory MPI subset), same shape / tile / ncomm, its natural fp32 projection and AllReduce."""
+    if rank != 0:
+        return None
+    W = WORKLOAD
+    base = dict(metric=METRIC, unit="ms", n_gpus=world_size, steps=args.steps, warmup=args.warmup,
+                higher_is_better=False, scaling="strong", vs_baseline=None, dtype="f16 in / f32 accumulate, projection and reduction in f32",
+                data="synthetic", impl="reference",
+                config=dict(workload=f"S={W['S']} H={W['H']} d_h={W['d_h']} causal tile={W['tile']} ncomm={W['ncomm']} TP={world_size}",
+                            mode=args.mode))
+    exe = os.path.join(ROOT, "oracle", "_ref", "attn_bench")
+    launch = os.path.join(ROOT, "oracle", "_ref", "efa_launch")
+    if not (os.path.exists(exe) and os.path.exists(launch)):
+        return dict(impl="reference", unavailable="oracle/_ref/attn_bench is not built (run __graft_entry__.build() where the reference sources are mounted)")
+    cmd = [launch, "-n", str(world_size), exe, "--S", str(W["S"]), "--H", str(W["H"]), "--d_h", str(W["d_h"]),
+           "--tile", str(W["tile"]), "--ncomm", str(W["ncomm"]), "--causal", "--modes", "attn,megatron,stream",
+           "--warmup", str(args.warmup), "--trials", str(args.steps)]
+    env = dict(os.environ)
+    for k in ("RANK", "LOCAL_RANK", "WORLD_SIZE", "MASTER_ADDR", "MASTER_PORT"):
+        env.pop(k, None)
+    try:
+        r = subprocess.run(cmd, capture_output=True, text=True, timeout=1500, env=env)
+    except subprocess.TimeoutExpired:
+        return dict(impl="reference", unavailable="the reference attn_bench did not finish within 1500 s")
+    if r.returncode != 0:
+        return dict(impl="reference", unavailable="reference attn_bench exited %d: %s" % (r.returncode, r.stderr.strip().splitlines()[-1:] or ""))
+    rows = {}
+    for line in r.stdout.splitlines():
+        f = line.split(",")
+        if len(f) >= 17 and f[0].isdigit():
+            rows[f[11]] = dict(min=float(f[12]), max=float(f[13]), mean=float(f[14]), median=float(f[15]), std=float(f[16]))
+    if args.mode not in rows:
+        return dict(impl="reference", unavailable="no %s row in the reference's output" % args.mode)
+    ms = rows[args.mode]["median"]
+    base.update(value=ms, ms_per_step=ms, tokens_per_s=W["S"] / (ms * 1e-3),
+                modes={k: v["median"] for k, v in rows.items()},
+                cpu_baseline=dict(value=ms, unit="ms", cores=0, kind="reference",
+                                  sample="the reference's own CUDA programs (it has no CPU implementation); whole workload, median of the timed trials"),
+                e2e=dict(value=ms, unit="ms", h2d_bytes_per_step=0, d2h_bytes_per_step=0),
+                gpu_launches=None)
+    return base
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--mode", default="stream", choices=["stream", "megatron"])
+    ap.add_argument("--reduce", default="nccl", choices=["nccl", "p2p"])
+    ap.add_argument("--cpu-rows", type=int, default=48, help="query rows of the CPU baseline sample (0 = skip)")
+    ap.add_argument("--S", type=int, default=WORKLOAD["S"], help="override the sequence length (profiling captures only)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.S == WORKLOAD["S"] else args.warmup
+
+    rank = int(os.environ.get("RANK", 0))
+    world_size = int(os.environ.get("WORLD_SIZE", 1))
+    local_rank = int(os.environ.get("LOCAL_RANK", 0))
+    if args.gpus != world_size and rank == 0 and world_size > 1:
+        print(f"warning: --gpus {args.gpus} but WORLD_SIZE={world_size}", file=sys.stderr)
+
+    if args.impl == "reference":
+        line = run_reference(args, world_size, rank)
+        if line is not None:
+            print(json.dumps(line), flush=True)
+        return 0
+
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as entry
+
+    pkg = entry.load_package()
+    pkg.lib()                                   # fails loudly when the CUDA library is not built
+    torch.cuda.set_device(local_rank)
+    if world_size > 1:
+        dist.init_process_group(backend="cpu:gloo,cuda:nccl", device_id=torch.device("cuda", local_rank))
+        world = pkg.World.from_torch(None, local_device=local_rank)
+    else:
+        world = pkg.World(0, 1, local_rank)
+
+    W = dict(WORKLOAD)
+    W["S"] = args.S
+    d = W["H"] * W["d_h"]
+    p = pkg.make_params(W["S"], d, W["H"], W["tile"], W["nbuf"], W["split"], W["causal"], world_size)
+    why = pkg.attn_check_params(p)
+    if why:
+        raise SystemExit(f"invalid workload for {world_size} ranks: {why}")
+    p.reduce = pkg.REDUCE_P2P if args.reduce == "p2p" else pkg.REDUCE_NCCL
+    mode = pkg.parse_mode(args.mode)
+
+    # Synthetic inputs in pinned host memory (N(0,1) Q/K/V, W_O ~ N(0, 1/d)), then resident copies.
+    qkv_shape = (p.H_local, p.S, p.d_h)
+    host = [torch.empty(qkv_shape, dtype=torch.float16).pin_memory() for _ in range(3)]
+    host.append(torch.empty((p.d_local, p.d), dtype=torch.float16).pin_memory())
+    host_out = torch.empty((p.S, p.d), dtype=torch.float16).pin_memory()
+    pkg.fill_host_inputs(p, rank, 42, pkg.RECIPE_NORMAL, *host)
+    dev = [h.cuda() for h in host]
+    out = torch.zeros((p.S, p.d), dtype=torch.float16, device="cuda")
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")      # > 126 MB L2
+    weights = pkg.Weights(*(t.data_ptr() for t in dev))
+    ctx = pkg.make_ctx(world, ncomm=W["ncomm"])
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world_size > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def one_step(host_path=False):
+        flush.fill_(rank + 1)                   # evict L2 between steps
+        barrier()
+        if host_path:
+            return pkg.run_mode_host(ctx, mode, *host, host_out, p)
+        return pkg.run_mode(ctx, mode, weights, out, p)
+
+    pkg.kernel_status_reset()
+    for _ in range(args.warmup):
+        one_step()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    stats = [one_step() for _ in range(args.steps)]
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    status = pkg.kernel_status()
+    if status[0] != 0:
+        raise SystemExit(f"rank {rank}: a kernel reported status {status}")
+    wall = [s.wall_ms for s in stats]           # each already the max over ranks
+    ms = statistics.mean(wall)
+    attn_ms = statistics.median([s.attn_kernel_ms for s in stats])
+    launches = stats[-1].kernel_launches
+
+    # other modes, for context (fewer steps)
+    modes = {args.mode: statistics.median(wall)}
+    for other in ("attn", "megatron", "stream"):
+        if other == args.mode:
+            continue
+        m = pkg.parse_mode(other)
+        ts = []
+        for i in range(2 + min(args.steps, 5)):
+            flush.fill_(1)
+            barrier()
+            st = pkg.run_mode(ctx, m, weights, out, p)
+            if i >= 2:
+                ts.append(st.wall_ms)
+        modes[other] = statistics.median(ts)
+    # exposed communication: (T - T(--no_comm)) / T with the reference's diagnostic flag
+    exposed = None
+    if world_size > 1:
+        p.skip_comm = 1
+        ts = []
+        for i in range(2 + min(args.steps, 5)):
+            flush.fill_(1)
+            barrier()
+            st = pkg.run_mode(ctx, mode, weights, out, p)
+            if i >= 2:
+                ts.append(st.wall_ms)
+        p.skip_comm = 0
+        t_nc = statistics.median(ts)
+        exposed = max(0.0, (statistics.median(wall) - t_nc) / statistics.median(wall))
+
+    # end to end through the host-buffer entry point
+    for _ in range(2):
+        one_step(host_path=True)
+    e2e_ms = statistics.mean([one_step(host_path=True).wall_ms for _ in range(max(3, min(args.steps, 10)))])
+    h2d = sum(h.numel() * 2 for h in host)
+    d2h = host_out.numel() * 2
+
+    pk = measured_peaks()
+    fl = attention_flops(p.S, p.d_h, p.H_local, p.causal)
+    achieved = fl / (attn_ms * 1e-3) / 1e12 if attn_ms > 0 else 0.0
+    proj_fl = 2.0 * p.S * p.d_local * p.d
+    link_bytes = 2.0 * (world_size - 1) / world_size * p.S * p.d * 2
+    t_roof = max((fl + proj_fl) / (pk["tflops"] * 1e12), link_bytes / 770e9) * 1e3
+
+    line = None
+    if rank == 0:
+        cpu = None
+        if args.cpu_rows > 0:
+            oracle = entry.load_oracle()
+            cpu = cpu_baseline(pkg, oracle, p, [h.numpy().view(np.uint16) for h in host], args.cpu_rows)
+        line = dict(
+            metric=METRIC, value=ms, unit="ms", n_gpus=world_size, steps=args.steps, warmup=args.warmup,
+            ms_per_step=ms, higher_is_better=False, scaling="strong", vs_baseline=None, dtype="f16 (f32 accumulate)",
+            data="synthetic",
+            config=dict(workload=f"S={p.S} H={p.H} d_h={p.d_h} causal tile={p.tile} ncomm={W['ncomm']} TP={world_size}",
+                        mode=args.mode, reduce=args.reduce, l2="256 MB buffer written between steps",
+                        inputs="Q,K,V ~ N(0,1) fp16 [H_local][S][d_h]; W_O ~ N(0,1/d) fp16; seed 42"),
+            tokens_per_s=p.S / (ms * 1e-3),
+            modes_ms=modes, exposed_comm_frac=exposed,
+            block_roofline=dict(t_ms=t_roof, frac=t_roof / ms, peak=f"{pk['tflops']} TFLOP/s bf16 {pk['source']}; 770 GB/s NVLink measured"),
+            roofline=dict(bound="tensor", kernel="fa_fwd_kernel<128>", achieved=achieved, peak=pk["tflops"], unit="TFLOP/s",
+                          frac=achieved / pk["tflops"], peak_source=f"of {pk['source']} (burst bf16)",
+                          frac_sustained=achieved / pk["tflops_sustained"], attn_kernel_ms=attn_ms,
+                          algorithmic_flops=fl, traffic=None),
+            cpu_baseline=cpu,
+            e2e=dict(value=e2e_ms, unit="ms", h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h),
+            gpu_launches=launches * args.steps,
+            clocks=clocks,
+        )
+    pkg.destroy_ctx(ctx)
+    if world_size > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if line is not None:
+        print(json.dumps(line), flush=True)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,135 @@
+// extern "C" surface of the library: argument checks, then the C++ implementation.
+#include "fa_fwd_sm100.cuh"
+#include "host_util.h"
+#include "runtime.h"
+
+#include <chrono>
+#include <cstring>
+
+using namespace efa;
+
+extern "C" int efa_abi_version(void) { return EFA_ABI_VERSION; }
+extern "C" const char* efa_last_error(void) { return last_error(); }
+
+extern "C" int efa_flash_attn_tc_forward(const void* Q, const void* K, const void* V,
+                                         void* O, int o_dtype, const efa_flash_partials* part,
+                                         int q_start, int q_rows, const efa_flash_params* p, void* stream,
+                                         int* tile_counters, int tile_rows)
+{
+    if (!Q || !K || !V || !p) { set_error("efa_flash_attn_tc_forward: null argument"); return 2; }
+    return fa_forward(Q, K, V, O, o_dtype, part, q_start, q_rows, *p, (cudaStream_t)stream, tile_counters, tile_rows);
+}
+
+extern "C" int efa_flash_attn_tc_combine(const efa_flash_partials* part, void* O, int o_dtype,
+                                         int row0, int rows, const efa_flash_params* p, void* stream)
+{
+    if (!part || !O || !p) { set_error("efa_flash_attn_tc_combine: null argument"); return 2; }
+    if (o_dtype != EFA_F32 && o_dtype != EFA_F16) { set_error("efa_flash_attn_tc_combine: unknown dtype"); return 2; }
+    return fa_combine(*part, O, o_dtype, row0, rows, *p, (cudaStream_t)stream);
+}
+
+extern "C" const char* efa_flash_attn_tc_check_params(const efa_flash_params* p, int q_rows)
+{
+    if (!p) return "null params";
+    return fa_check_params(*p, q_rows);
+}
+
+extern "C" int efa_convert_f32_to_f16(const float* in, void* out, size_t n, void* stream)
+{
+    if ((!in || !out) && n) { set_error("efa_convert_f32_to_f16: null argument"); return 2; }
+    return convert_f32_to_f16_dev(in, out, n, (cudaStream_t)stream);
+}
+
+extern "C" int efa_project_f16(const void* O_tile, const void* W_O, void* out, int rows, int d_local, int d, void* stream)
+{
+    return project_f16(O_tile, W_O, out, rows, d_local, d, (cudaStream_t)stream);
+}
+
+extern "C" int efa_kernel_status(int* out4)
+{
+    if (!out4) { set_error("efa_kernel_status: null argument"); return 2; }
+    int* w = kernel_status_word();
+    if (!w) { set_error("efa_kernel_status: no status word (no device?)"); return 1; }
+    EFA_CUDA(cudaMemcpy(out4, w, 4 * sizeof(int), cudaMemcpyDeviceToHost));
+    return 0;
+}
+
+extern "C" int efa_kernel_status_reset(void)
+{
+    int* w = kernel_status_word();
+    if (!w) { set_error("efa_kernel_status_reset: no status word (no device?)"); return 1; }
+    EFA_CUDA(cudaMemset(w, 0, 4 * sizeof(int)));
+    return 0;
+}
+
+extern "C" int efa_run_mode(efa_ctx* ctx, int mode, const efa_weights* w, void* output,
+                            const efa_params* p, efa_run_stats* stats)
+{
+    if (!ctx || !w || !p) { set_error("efa_run_mode: null argument"); return 2; }
+    return run_mode_impl(ctx, mode, *w, output, *p, stats);
+}
+
+extern "C" int efa_run_mode_host(efa_ctx* c, int mode,
+                                 const uint16_t* Qh, const uint16_t* Kh, const uint16_t* Vh, const uint16_t* W_O,
+                                 uint16_t* output, const efa_params* p, efa_run_stats* stats)
+{
+    if (!c || !Qh || !Kh || !Vh || !W_O || !p) { set_error("efa_run_mode_host: null argument"); return 2; }
+    const size_t qkv = (size_t)p->H_local * p->S * p->d_h * 2;
+    const size_t wb = (size_t)p->d_local * p->d * 2;
+    const size_t ob = (size_t)p->S * p->d * 2;
+    {
+        size_t a = c->h_qkv_bytes, b = c->h_qkv_bytes, d = c->h_qkv_bytes;
+        if (ensure_bytes(&c->h_Q, &a, qkv) || ensure_bytes(&c->h_K, &b, qkv) || ensure_bytes(&c->h_V, &d, qkv)) return 1;
+        c->h_qkv_bytes = a < b ? (a < d ? a : d) : (b < d ? b : d);
+        if (ensure_bytes(&c->h_W, &c->h_w_bytes, wb) || ensure_bytes(&c->h_out, &c->h_out_bytes, ob)) return 1;
+    }
+    if (world_barrier(c->world)) return 1;
+    const auto t0 = std::chrono::steady_clock::now();
+    cudaStream_t s = c->compute_stream;
+    EFA_CUDA(cudaMemcpyAsync(c->h_Q, Qh, qkv, cudaMemcpyHostToDevice, s));
+    EFA_CUDA(cudaMemcpyAsync(c->h_K, Kh, qkv, cudaMemcpyHostToDevice, s));
+    EFA_CUDA(cudaMemcpyAsync(c->h_V, Vh, qkv, cudaMemcpyHostToDevice, s));
+    EFA_CUDA(cudaMemcpyAsync(c->h_W, W_O, wb, cudaMemcpyHostToDevice, s));
+    EFA_CUDA(cudaStreamSynchronize(s));
+    efa_weights w{c->h_Q, c->h_K, c->h_V, c->h_W};
+    efa_run_stats inner;
+    std::memset(&inner, 0, sizeof(inner));
+    if (run_mode_impl(c, mode, w, c->h_out, *p, &inner)) return 1;
+    if (output && mode != EFA_MODE_ATTN && mode != EFA_MODE_ATTN_TILED) {
+        EFA_CUDA(cudaMemcpyAsync(output, c->h_out, ob, cudaMemcpyDeviceToHost, s));
+        EFA_CUDA(cudaStreamSynchronize(s));
+    }
+    double ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+    if (world_max(c->world, &ms)) return 1;
+    if (stats) { *stats = inner; stats->wall_ms = ms; }
+    return 0;
+}
+
+extern "C" int efa_world_selftest(const efa_world* w)
+{
+    if (!w) { set_error("efa_world_selftest: null world"); return 2; }
+    if (w->size <= 1) return 0;
+    if (!w->barrier || !w->allreduce_max_f64 || !w->bcast_bytes || !w->allgather_bytes) {
+        set_error("efa_world_selftest: a callback is missing");
+        return 2;
+    }
+    if (w->barrier(w->user)) { set_error("efa_world_selftest: barrier failed"); return 1; }
+    double v = 10.0 + w->rank;
+    if (w->allreduce_max_f64(w->user, &v) || v != 10.0 + (w->size - 1)) {
+        set_error("efa_world_selftest: max gave %g, expected %g", v, 10.0 + (w->size - 1));
+        return 1;
+    }
+    unsigned char buf[128];
+    for (int i = 0; i < 128; i++) buf[i] = (unsigned char)(w->rank == 0 ? (i * 7 + 3) : 0);
+    if (w->bcast_bytes(w->user, buf, sizeof(buf), 0)) { set_error("efa_world_selftest: broadcast failed"); return 1; }
+    for (int i = 0; i < 128; i++)
+        if (buf[i] != (unsigned char)(i * 7 + 3)) { set_error("efa_world_selftest: broadcast byte %d wrong", i); return 1; }
+    unsigned char mine[64], all[64 * 64];
+    if (w->size > 64) { set_error("efa_world_selftest: more than 64 ranks"); return 2; }
+    for (int i = 0; i < 64; i++) mine[i] = (unsigned char)(w->rank * 3 + i);
+    if (w->allgather_bytes(w->user, mine, all, sizeof(mine))) { set_error("efa_world_selftest: all-gather failed"); return 1; }
+    for (int r = 0; r < w->size; r++)
+        for (int i = 0; i < 64; i++)
+            if (all[r * 64 + i] != (unsigned char)(r * 3 + i)) { set_error("efa_world_selftest: all-gather slot %d wrong", r); return 1; }
+    return 0;
+}

@@ -1,0 +1,533 @@
+// FlashAttention forward for sm_100a: fp16 Q/K/V, fp32 accumulate in tensor memory, fp32 or fp16 O.
+//
+// Stands in for flash_attn_tc_kernel / flash_attn_tc_forward of eager-flash-attention
+// (flash_attn_tc.cu:73-312, 363-399) behind the same launch interface: same tensor layouts, same
+// split-KV partial format (row max in the log2 domain), same per-tile completion counters.
+//
+// One CTA = 128 query rows of one (head, split). K and V stream through shared memory in 128-key
+// stages filled by TMA (128/64/32-byte swizzle chosen from d_h). S = Q K^T is a tcgen05.mma with both
+// operands in shared memory and the 128x128 fp32 result in tensor memory; each of the 128 threads owns
+// one row of S (tcgen05.ld 32x32b), does the online softmax for that row without any shuffle,
+// and writes P as fp16 back into tensor memory over S. O += P V is a tcgen05.mma with A = P from tensor
+// memory and B = V from shared memory in MN-major form; O stays in tensor memory for the whole
+// key sweep and is rescaled there only when a row maximum moved.
+#include "fa_fwd_sm100.cuh"
+#include "host_util.h"
+#include "sm100_ptx.cuh"
+
+#include <cmath>
+#include <cstdio>
+#include <map>
+#include <mutex>
+#include <tuple>
+
+namespace efa {
+
+namespace {
+
+constexpr int FA_BM = 128;      // query rows per CTA
+constexpr int FA_BN = 128;      // keys per stage
+constexpr float kNegInf = -INFINITY;
+
+template <int D>
+struct FaCfg {
+    static constexpr int SWB        = D >= 64 ? 128 : D * 2;     // swizzle width = TMA box row, bytes
+    static constexpr int BOXC       = SWB / 2;                   // fp16 columns per box
+    static constexpr int NBOX       = D / BOXC;                  // boxes per 128-row tile (2 when D = 128)
+    static constexpr int BOX_BYTES  = 128 * SWB;
+    static constexpr int TILE_BYTES = 128 * D * 2;
+    static constexpr int NSTAGE     = D == 128 ? 1 : 2;
+    static constexpr int SMEM_BYTES = TILE_BYTES * (1 + 2 * NSTAGE) + 1024;   // + alignment slack
+    static constexpr int TMEM_COLS  = 256;                       // S/P: 128 columns, O: D columns
+    static constexpr int OCH        = D >= 32 ? 32 : 16;         // O columns per tcgen05.ld
+};
+
+struct FaArgs {
+    float*  O32;
+    __half* O16;
+    float*  O_part;
+    float*  m_part;
+    float*  l_part;
+    int     part_rows;
+    int     q_start, q_rows, S, H_local, nsplit, kv_len, causal;
+    float   scale_log2e;
+    int*    tile_counters;
+    int     tile_rows;
+    int*    status;
+};
+
+__device__ __forceinline__ float ex2(float x)
+{
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+template <int D, bool OUT_F16>
+__global__ void __launch_bounds__(128)
+fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ,
+              const __grid_constant__ CUtensorMap tmK,
+              const __grid_constant__ CUtensorMap tmV,
+              const FaArgs a)
+{
+    using C = FaCfg<D>;
+    constexpr uint32_t SWZ = swizzle_code(C::SWB);
+    constexpr uint32_t IDESC_QK = idesc_f16_f32(FA_BM, FA_BN, 0, 0);
+    constexpr uint32_t IDESC_PV = idesc_f16_f32(FA_BM, D, 0, 1);
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* sQ = smem;
+    uint8_t* sK = sQ + C::TILE_BYTES;
+    uint8_t* sV = sK + C::NSTAGE * C::TILE_BYTES;
+
+    __shared__ __align__(8) uint64_t bar_q;
+    __shared__ __align__(8) uint64_t bar_k[C::NSTAGE];
+    __shared__ __align__(8) uint64_t bar_v[C::NSTAGE];
+    __shared__ __align__(8) uint64_t bar_s;
+    __shared__ uint32_t tmem_base_smem;
+    __shared__ int abort_word;
+
+    const int tid  = threadIdx.x;
+    const int warp = tid >> 5;
+
+    // x enumerates (head, split) pairs, y the 128-row blocks: blocks are dispatched in query-row order.
+    const int head  = blockIdx.x % a.H_local;
+    const int split = blockIdx.x / a.H_local;
+    const int block_row0 = blockIdx.y * FA_BM;                     // first row of this block within the launch
+    const int rows_valid = min(FA_BM, a.q_rows - block_row0);      // 64 or 128
+    const int q_abs0 = a.q_start + block_row0;                     // absolute index of the block's first row
+    const int kv_lo = split * a.kv_len;
+    const int kv_hi = kv_lo + a.kv_len;
+    const int kv_end = a.causal ? min(kv_hi, q_abs0 + rows_valid) : kv_hi;
+    const int nblk = kv_end > kv_lo ? (kv_end - kv_lo + FA_BN - 1) / FA_BN : 0;
+
+    if (tid == 0) {
+        abort_word = 0;
+        mbar_init(&bar_q, 1);
+        for (int s = 0; s < C::NSTAGE; s++) { mbar_init(&bar_k[s], 1); mbar_init(&bar_v[s], 1); }
+        mbar_init(&bar_s, 1);
+        mbar_fence_init();
+        tma_prefetch_desc(&tmQ);
+        tma_prefetch_desc(&tmK);
+        tma_prefetch_desc(&tmV);
+    }
+    __syncwarp();
+    if (warp == 0) tmem_alloc(&tmem_base_smem, C::TMEM_COLS);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+
+    const uint32_t tmem_base = tmem_base_smem;
+    const uint32_t tmem_S = tmem_base;            // fp32 S, 128 columns; P (fp16 pairs) reuses columns 0..63
+    const uint32_t tmem_O = tmem_base + 128;      // fp32 O, D columns
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;   // this warp's 32 TMEM lanes
+
+    auto load_tile = [&](uint8_t* dst, const CUtensorMap* tm, uint64_t* bar, int row) {
+        mbar_expect_tx(bar, C::TILE_BYTES);
+        #pragma unroll
+        for (int b = 0; b < C::NBOX; b++)
+            tma_load_3d(dst + b * C::BOX_BYTES, tm, bar, b * C::BOXC, row, head);
+    };
+    auto issue_qk = [&](int stage) {
+        const uint32_t qa = smem_u32(sQ);
+        const uint32_t ka = smem_u32(sK + stage * C::TILE_BYTES);
+        #pragma unroll
+        for (int ks = 0; ks < D / 16; ks++) {
+            const uint32_t off = (uint32_t)((ks * 16) / C::BOXC) * C::BOX_BYTES + (uint32_t)((ks * 16) % C::BOXC) * 2u;
+            tc_mma_ss(tmem_S, smem_desc(qa + off, 16, 8 * C::SWB, SWZ), smem_desc(ka + off, 16, 8 * C::SWB, SWZ),
+                      IDESC_QK, ks > 0 ? 1u : 0u);
+        }
+    };
+    auto issue_pv = [&](int stage, bool first) {
+        const uint32_t va = smem_u32(sV + stage * C::TILE_BYTES);
+        #pragma unroll
+        for (int ks = 0; ks < FA_BN / 16; ks++) {
+            // 16 keys = two 8-row groups of the MN-major layout; column blocks (D = 128) are BOX_BYTES apart.
+            tc_mma_ts(tmem_O, tmem_S + ks * 8, smem_desc(va + ks * 16 * C::SWB, C::BOX_BYTES, 8 * C::SWB, SWZ),
+                      IDESC_PV, (!first || ks > 0) ? 1u : 0u);
+        }
+    };
+
+    float m_run = kNegInf;     // running row max, already multiplied by scale*log2(e)
+    float l_run = 0.f;         // running row denominator
+    bool  failed = false;
+
+    if (nblk > 0) {
+        if (tid == 0) {
+            load_tile(sQ, &tmQ, &bar_q, q_abs0);
+            for (int s = 0; s < C::NSTAGE && s < nblk; s++)
+                load_tile(sK + s * C::TILE_BYTES, &tmK, &bar_k[s], kv_lo + s * FA_BN);
+            for (int s = 0; s + 1 < C::NSTAGE && s < nblk; s++)
+                load_tile(sV + s * C::TILE_BYTES, &tmV, &bar_v[s], kv_lo + s * FA_BN);
+            if (mbar_wait(&bar_q, 0, &abort_word, 1) && mbar_wait(&bar_k[0], 0, &abort_word, 2)) {
+                tc_fence_after_sync();
+                issue_qk(0);
+                tc_commit(&bar_s);
+            }
+        }
+
+        for (int j = 0; j < nblk; j++) {
+            const int stage = j % C::NSTAGE;
+            const int kb = kv_lo + j * FA_BN;                       // first key of this stage
+
+            bool ok = mbar_wait(&bar_s, (uint32_t)(j & 1), &abort_word, 3);
+            if (__syncthreads_or((!ok) || abort_word != 0)) { failed = true; break; }
+            tc_fence_after_sync();
+
+            // S(j) is complete, hence so are QK(j) and PV(j-1): K stage `stage` and the V stage
+            // used by block j-1 are free again.
+            if (tid == 0) {
+                if (j + C::NSTAGE < nblk)
+                    load_tile(sK + stage * C::TILE_BYTES, &tmK, &bar_k[stage], kv_lo + (j + C::NSTAGE) * FA_BN);
+                const int vb = j + C::NSTAGE - 1;
+                if (vb < nblk && vb >= C::NSTAGE - 1)
+                    load_tile(sV + (vb % C::NSTAGE) * C::TILE_BYTES, &tmV, &bar_v[vb % C::NSTAGE], kv_lo + vb * FA_BN);
+            }
+
+            // ---- this thread's row of S -> registers
+            uint32_t su[4][32];
+            #pragma unroll
+            for (int c = 0; c < 4; c++) tmem_ld32(tmem_S + lane_base + c * 32, su[c]);
+            tmem_wait_ld();
+
+            const bool need_mask = (kb + FA_BN > kv_hi) || (a.causal && kb + FA_BN - 1 > q_abs0);
+            if (need_mask) {
+                int lim = kv_hi - 1 - kb;                            // last admissible column of this stage
+                if (a.causal) lim = min(lim, q_abs0 + tid - kb);
+                #pragma unroll
+                for (int c = 0; c < 4; c++)
+                    #pragma unroll
+                    for (int i = 0; i < 32; i++)
+                        if (c * 32 + i > lim) su[c][i] = 0xff800000u;   // -inf
+            }
+
+            float mx = kNegInf;
+            #pragma unroll
+            for (int c = 0; c < 4; c++)
+                #pragma unroll
+                for (int i = 0; i < 32; i++) mx = fmaxf(mx, __uint_as_float(su[c][i]));
+
+            const float m_new = fmaxf(m_run, mx * a.scale_log2e);
+            const float m_use = (m_new == kNegInf) ? 0.f : m_new;    // rows with no admissible key yet
+            const float alpha = ex2(m_run - m_use);                  // 0 on the first stage
+            float psum = 0.f;
+            #pragma unroll
+            for (int c = 0; c < 4; c++) {
+                uint32_t pk[16];
+                #pragma unroll
+                for (int i = 0; i < 16; i++) {
+                    const float p0 = ex2(fmaf(__uint_as_float(su[c][2 * i]),     a.scale_log2e, -m_use));
+                    const float p1 = ex2(fmaf(__uint_as_float(su[c][2 * i + 1]), a.scale_log2e, -m_use));
+                    psum += p0 + p1;
+                    pk[i] = pack_f16x2(p0, p1);
+                }
+                tmem_st16(tmem_S + lane_base + c * 16, pk);
+            }
+            l_run = l_run * alpha + psum;
+            m_run = m_new;
+
+            // ---- rescale the O accumulator when some row of this warp moved its maximum
+            if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+                #pragma unroll
+                for (int c = 0; c < D / C::OCH; c++) {
+                    if constexpr (C::OCH == 32) {
+                        uint32_t o[32];
+                        tmem_ld32(tmem_O + lane_base + c * 32, o);
+                        tmem_wait_ld();
+                        #pragma unroll
+                        for (int i = 0; i < 32; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tmem_st32(tmem_O + lane_base + c * 32, o);
+                    } else {
+                        uint32_t o[16];
+                        tmem_ld16(tmem_O + lane_base + c * 16, o);
+                        tmem_wait_ld();
+                        #pragma unroll
+                        for (int i = 0; i < 16; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tmem_st16(tmem_O + lane_base + c * 16, o);
+                    }
+                }
+            }
+            tmem_wait_st();
+            tc_fence_before_sync();
+            __syncthreads();
+
+            if (tid == 0) {
+                tc_fence_after_sync();
+                if (mbar_wait(&bar_v[stage], (uint32_t)((j / C::NSTAGE) & 1), &abort_word, 4)) {
+                    issue_pv(stage, j == 0);
+                    bool issue_ok = true;
+                    if (j + 1 < nblk) {
+                        const int ns = (j + 1) % C::NSTAGE;
+                        issue_ok = mbar_wait(&bar_k[ns], (uint32_t)(((j + 1) / C::NSTAGE) & 1), &abort_word, 5);
+                        if (issue_ok) issue_qk(ns);
+                    }
+                    if (issue_ok) tc_commit(&bar_s);
+                }
+            }
+        }
+
+        if (!failed) {
+            bool ok = mbar_wait(&bar_s, (uint32_t)(nblk & 1), &abort_word, 6);
+            if (__syncthreads_or((!ok) || abort_word != 0)) failed = true;
+            tc_fence_after_sync();
+        }
+    }
+
+    // ---- epilogue: this thread's row of O
+    if (!failed && tid < rows_valid) {
+        const size_t ld_o = (size_t)a.H_local * D;
+        const size_t row = (size_t)block_row0 + tid;
+        const float inv = (a.nsplit == 1) ? 1.f / l_run : 1.f;
+        float*  dst32 = nullptr;
+        __half* dst16 = nullptr;
+        if (a.nsplit == 1) {
+            if constexpr (OUT_F16) dst16 = a.O16 + row * ld_o + (size_t)head * D;
+            else                   dst32 = a.O32 + row * ld_o + (size_t)head * D;
+        } else {
+            dst32 = a.O_part + ((size_t)split * a.part_rows + row) * ld_o + (size_t)head * D;
+            const size_t s0 = ((size_t)split * a.part_rows + row) * a.H_local + head;
+            a.m_part[s0] = m_run;
+            a.l_part[s0] = l_run;
+        }
+        #pragma unroll
+        for (int c = 0; c < D / 16; c++) {
+            uint32_t o[16];
+            if (nblk > 0) {
+                tmem_ld16(tmem_O + lane_base + c * 16, o);
+                tmem_wait_ld();
+            } else {
+                #pragma unroll
+                for (int i = 0; i < 16; i++) o[i] = 0u;
+            }
+            if (dst16) {
+                uint4 v0, v1;
+                v0.x = pack_f16x2(__uint_as_float(o[0]) * inv,  __uint_as_float(o[1]) * inv);
+                v0.y = pack_f16x2(__uint_as_float(o[2]) * inv,  __uint_as_float(o[3]) * inv);
+                v0.z = pack_f16x2(__uint_as_float(o[4]) * inv,  __uint_as_float(o[5]) * inv);
+                v0.w = pack_f16x2(__uint_as_float(o[6]) * inv,  __uint_as_float(o[7]) * inv);
+                v1.x = pack_f16x2(__uint_as_float(o[8]) * inv,  __uint_as_float(o[9]) * inv);
+                v1.y = pack_f16x2(__uint_as_float(o[10]) * inv, __uint_as_float(o[11]) * inv);
+                v1.z = pack_f16x2(__uint_as_float(o[12]) * inv, __uint_as_float(o[13]) * inv);
+                v1.w = pack_f16x2(__uint_as_float(o[14]) * inv, __uint_as_float(o[15]) * inv);
+                uint4* d = reinterpret_cast<uint4*>(dst16 + c * 16);
+                d[0] = v0;
+                d[1] = v1;
+            } else {
+                float4* d = reinterpret_cast<float4*>(dst32 + c * 16);
+                #pragma unroll
+                for (int q = 0; q < 4; q++)
+                    d[q] = make_float4(__uint_as_float(o[4 * q]) * inv, __uint_as_float(o[4 * q + 1]) * inv,
+                                       __uint_as_float(o[4 * q + 2]) * inv, __uint_as_float(o[4 * q + 3]) * inv);
+            }
+        }
+    }
+    // rows_valid is 64 or 128, so a warp takes the branch above as a whole and every tcgen05.ld in it
+    // is executed by a full warp.
+
+    // ---- signal tile completion: one count per finished 64-row block, after the rows are visible
+    if (!failed && a.tile_counters != nullptr) {
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) {
+            for (int sb = 0; sb < rows_valid; sb += 64)
+                atomicAdd(a.tile_counters + (block_row0 + sb) / a.tile_rows, 1);
+        }
+    }
+
+    // ---- teardown
+    if (failed) {
+        // Give copies that may still be in flight time to land before the shared memory is released.
+        for (int i = 0; i < 64; i++) __nanosleep(100000);
+        if (tid == 0 && a.status != nullptr) {
+            if (atomicCAS(a.status, 0, (int)KS_WAIT_TIMEOUT) == 0) {
+                a.status[1] = (int)(blockIdx.y * gridDim.x + blockIdx.x);
+                a.status[2] = abort_word;
+            }
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem_base, C::TMEM_COLS);
+}
+
+// One thread per (row, column pair): O = sum_i 2^(m_i - M) O_i / sum_i 2^(m_i - M) l_i
+template <bool OUT_F16>
+__global__ void combine_splits_kernel(const float* __restrict__ O_part, const float* __restrict__ m_part,
+                                      const float* __restrict__ l_part, void* __restrict__ O,
+                                      int row0, int rows, int ws_rows, int d_local, int H_local, int d_h, int split)
+{
+    const int pairs = d_local / 2;
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long)rows * pairs) return;
+    const int r = (int)(idx / pairs);
+    const int col = (int)(idx % pairs) * 2;
+    const int head = col / d_h;
+    const size_t row = (size_t)row0 + r;
+
+    float M = -INFINITY;
+    for (int i = 0; i < split; i++)
+        M = fmaxf(M, m_part[((size_t)i * ws_rows + row) * H_local + head]);
+    float L = 0.f, ax = 0.f, ay = 0.f;
+    for (int i = 0; i < split; i++) {
+        const size_t s = ((size_t)i * ws_rows + row) * H_local + head;
+        const float w = exp2f(m_part[s] - M);
+        L += w * l_part[s];
+        const float2 v = *reinterpret_cast<const float2*>(O_part + ((size_t)i * ws_rows + row) * d_local + col);
+        ax += w * v.x;
+        ay += w * v.y;
+    }
+    const float inv = 1.f / L;
+    if constexpr (OUT_F16) {
+        *reinterpret_cast<__half2*>(reinterpret_cast<__half*>(O) + (size_t)r * d_local + col) =
+            __floats2half2_rn(ax * inv, ay * inv);
+    } else {
+        *reinterpret_cast<float2*>(reinterpret_cast<float*>(O) + (size_t)r * d_local + col) = make_float2(ax * inv, ay * inv);
+    }
+}
+
+__global__ void f32_to_f16_kernel(const float* __restrict__ in, __half* __restrict__ out, size_t n)
+{
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) out[i] = __float2half_rn(in[i]);
+}
+
+// Tensor maps depend only on (pointer, S, H_local, d_h); drivers launch the same tensors over and over.
+struct TmapKey {
+    const void* ptr; int S, H, D;
+    bool operator<(const TmapKey& o) const { return std::tie(ptr, S, H, D) < std::tie(o.ptr, o.S, o.H, o.D); }
+};
+
+int get_qkv_tmap(const void* ptr, int S, int H_local, int D, CUtensorMap* out)
+{
+    static std::map<TmapKey, CUtensorMap> cache;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    TmapKey key{ptr, S, H_local, D};
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return 0; }
+    const int boxc = D >= 64 ? 64 : D;
+    unsigned long long dims[3] = {(unsigned long long)D, (unsigned long long)S, (unsigned long long)H_local};
+    unsigned long long strides[2] = {(unsigned long long)D * 2ull, (unsigned long long)S * D * 2ull};
+    unsigned box[3] = {(unsigned)boxc, 128u, 1u};
+    CUtensorMap tm;
+    if (make_tmap_f16(&tm, ptr, 3, dims, strides, box)) return 1;
+    if (cache.size() > 256) cache.clear();
+    cache[key] = tm;
+    *out = tm;
+    return 0;
+}
+
+template <int D, bool OUT_F16>
+int launch_fa(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FaArgs& args,
+              dim3 grid, cudaStream_t stream)
+{
+    using C = FaCfg<D>;
+    static bool configured[64] = {};
+    int dev = 0;
+    EFA_CUDA(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        EFA_CUDA(cudaFuncSetAttribute(fa_fwd_kernel<D, OUT_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+        configured[dev] = true;
+    }
+    fa_fwd_kernel<D, OUT_F16><<<grid, 128, C::SMEM_BYTES, stream>>>(tq, tk, tv, args);
+    EFA_CUDA(cudaGetLastError());
+    return 0;
+}
+
+}  // namespace
+
+const char* fa_check_params(const efa_flash_params& p, int q_rows)
+{
+    if (p.d_h != 16 && p.d_h != 32 && p.d_h != 64 && p.d_h != 128)
+        return "tc: d_h must be 16, 32, 64 or 128";
+    if (p.S <= 0 || p.S % 64 != 0) return "tc: S must be a multiple of 64";
+    if (q_rows <= 0 || q_rows % 64 != 0) return "tc: tile must be a multiple of 64";
+    if (p.split < 1 || p.S % (p.split * 64) != 0) return "tc: S must be a multiple of split * 64";
+    if (p.H_local < 1) return "tc: H_local must be positive";
+    return nullptr;
+}
+
+int fa_forward(const void* Q, const void* K, const void* V, void* O, int o_dtype,
+               const efa_flash_partials* part, int q_start, int q_rows,
+               const efa_flash_params& p, cudaStream_t stream, int* tile_counters, int tile_rows)
+{
+    if (const char* why = fa_check_params(p, q_rows)) { set_error("flash_attn_tc_forward: %s", why); return 2; }
+    if (q_start < 0 || q_start % 64 != 0 || q_start + q_rows > p.S) {
+        set_error("flash_attn_tc_forward: rows [%d, %d) outside [0, %d) or not 64-aligned", q_start, q_start + q_rows, p.S);
+        return 2;
+    }
+    if (tile_counters != nullptr && (tile_rows <= 0 || tile_rows % 64 != 0)) {
+        set_error("flash_attn_tc_forward: tile_rows must be a positive multiple of 64 when counters are given");
+        return 2;
+    }
+    if (o_dtype != EFA_F32 && o_dtype != EFA_F16) { set_error("flash_attn_tc_forward: unknown O dtype %d", o_dtype); return 2; }
+    if (p.split > 1) {
+        if (!part || !part->O_part || !part->m_part || !part->l_part || part->rows < q_rows) {
+            set_error("flash_attn_tc_forward: split > 1 needs a partials workspace sized for the launch rows");
+            return 2;
+        }
+    } else if (O == nullptr) {
+        set_error("flash_attn_tc_forward: O is null");
+        return 2;
+    }
+
+    CUtensorMap tq, tk, tv;
+    if (get_qkv_tmap(Q, p.S, p.H_local, p.d_h, &tq) || get_qkv_tmap(K, p.S, p.H_local, p.d_h, &tk) ||
+        get_qkv_tmap(V, p.S, p.H_local, p.d_h, &tv))
+        return 1;
+
+    FaArgs a;
+    a.O32 = (o_dtype == EFA_F32) ? static_cast<float*>(O) : nullptr;
+    a.O16 = (o_dtype == EFA_F16) ? static_cast<__half*>(O) : nullptr;
+    a.O_part = part ? part->O_part : nullptr;
+    a.m_part = part ? part->m_part : nullptr;
+    a.l_part = part ? part->l_part : nullptr;
+    a.part_rows = part ? part->rows : 0;
+    a.q_start = q_start; a.q_rows = q_rows; a.S = p.S; a.H_local = p.H_local;
+    a.nsplit = p.split; a.kv_len = p.S / p.split; a.causal = p.causal;
+    a.scale_log2e = p.scale * 1.4426950408889634f;
+    a.tile_counters = tile_counters; a.tile_rows = tile_rows;
+    a.status = kernel_status_word();
+
+    dim3 grid(p.H_local * p.split, (q_rows + FA_BM - 1) / FA_BM);
+    const bool f16 = (o_dtype == EFA_F16);
+    switch (p.d_h) {
+        case 16:  return f16 ? launch_fa<16, true>(tq, tk, tv, a, grid, stream)  : launch_fa<16, false>(tq, tk, tv, a, grid, stream);
+        case 32:  return f16 ? launch_fa<32, true>(tq, tk, tv, a, grid, stream)  : launch_fa<32, false>(tq, tk, tv, a, grid, stream);
+        case 64:  return f16 ? launch_fa<64, true>(tq, tk, tv, a, grid, stream)  : launch_fa<64, false>(tq, tk, tv, a, grid, stream);
+        case 128: return f16 ? launch_fa<128, true>(tq, tk, tv, a, grid, stream) : launch_fa<128, false>(tq, tk, tv, a, grid, stream);
+    }
+    set_error("flash_attn_tc_forward: unsupported d_h=%d", p.d_h);
+    return 2;
+}
+
+int fa_combine(const efa_flash_partials& part, void* O, int o_dtype, int row0, int rows,
+               const efa_flash_params& p, cudaStream_t stream)
+{
+    if (p.split <= 1) return 0;
+    const int d_local = p.H_local * p.d_h;
+    const long total = (long)rows * (d_local / 2);
+    const int blocks = (int)((total + 255) / 256);
+    if (o_dtype == EFA_F16)
+        combine_splits_kernel<true><<<blocks, 256, 0, stream>>>(part.O_part, part.m_part, part.l_part, O,
+                                                                 row0, rows, part.rows, d_local, p.H_local, p.d_h, p.split);
+    else
+        combine_splits_kernel<false><<<blocks, 256, 0, stream>>>(part.O_part, part.m_part, part.l_part, O,
+                                                                  row0, rows, part.rows, d_local, p.H_local, p.d_h, p.split);
+    EFA_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int convert_f32_to_f16_dev(const float* in, void* out, size_t n, cudaStream_t stream)
+{
+    if (n == 0) return 0;
+    int blocks = (int)((n + 255) / 256);
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    f32_to_f16_kernel<<<blocks, 256, 0, stream>>>(in, static_cast<__half*>(out), n);
+    EFA_CUDA(cudaGetLastError());
+    return 0;
+}
+
+}  // namespace efa

@@ -1,0 +1,23 @@
+// Internal C++ interface of the attention kernels (the C ABI in efa_b200.h forwards to these).
+#pragma once
+
+#include <cuda_runtime.h>
+#include "../../include/efa_b200.h"
+
+namespace efa {
+
+const char* fa_check_params(const efa_flash_params& p, int q_rows);
+
+int fa_forward(const void* Q, const void* K, const void* V, void* O, int o_dtype,
+               const efa_flash_partials* part, int q_start, int q_rows,
+               const efa_flash_params& p, cudaStream_t stream, int* tile_counters, int tile_rows);
+
+int fa_combine(const efa_flash_partials& part, void* O, int o_dtype, int row0, int rows,
+               const efa_flash_params& p, cudaStream_t stream);
+
+int convert_f32_to_f16_dev(const float* in, void* out, size_t n, cudaStream_t stream);
+
+// out[rows][d] = A[rows][d_local] * W[d_local][d]; fp16 in, fp32 accumulate, fp16 out.
+int project_f16(const void* A, const void* W, void* out, int rows, int d_local, int d, cudaStream_t stream);
+
+}  // namespace efa

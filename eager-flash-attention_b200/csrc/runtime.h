@@ -1,0 +1,50 @@
+// Host runtime of one rank: problem description, streams and communicators, scratch memory.
+// Counterpart of attn_main.cu / attn_defs.cuh of eager-flash-attention for the fp16 data path.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <nccl.h>
+#include <vector>
+
+#include "../../include/efa_b200.h"
+
+#define EFA_MAX_COMM 8   /* MAX_COMM, attn_defs.cuh:90 */
+
+struct P2PState;   // peer-mapped staging of the fused reduction (p2p_reduce.cu)
+
+struct efa_ctx {
+    efa_world    world;
+    cudaStream_t compute_stream = nullptr;
+    cudaStream_t proj_stream = nullptr;
+    cudaStream_t comm_streams[EFA_MAX_COMM] = {};
+    ncclComm_t   nccls[EFA_MAX_COMM] = {};
+    int          ncomm = 0;
+
+    // Scratch, grown on demand and reused across run_mode calls (freed by efa_destroy_ctx).
+    void*  O_all = nullptr;     size_t O_all_bytes = 0;      // fp16 [S][d_local]
+    void*  send_buf = nullptr;  size_t send_bytes = 0;       // fp16 [S][d]
+    int*   counters = nullptr;  size_t counters_n = 0;
+    float* ws_O = nullptr; float* ws_m = nullptr; float* ws_l = nullptr;
+    size_t ws_O_n = 0, ws_ml_n = 0;
+    std::vector<cudaEvent_t> events;                        // disable-timing events, one per tile + a few
+    cudaEvent_t ev_t0 = nullptr, ev_t1 = nullptr, ev_t2 = nullptr, ev_t3 = nullptr;   // timing events
+
+    // Device staging of efa_run_mode_host.
+    void* h_Q = nullptr; void* h_K = nullptr; void* h_V = nullptr; void* h_W = nullptr; void* h_out = nullptr;
+    size_t h_qkv_bytes = 0, h_w_bytes = 0, h_out_bytes = 0;
+
+    P2PState* p2p = nullptr;
+};
+
+namespace efa {
+
+int world_barrier(const efa_world& w);
+int world_max(const efa_world& w, double* v);
+
+// Grow-only scratch helpers; return 0 on success.
+int ensure_bytes(void** ptr, size_t* have, size_t want);
+int ensure_events(efa_ctx* c, size_t n);
+
+int run_mode_impl(efa_ctx* c, int mode, const efa_weights& w, void* output, const efa_params& p, efa_run_stats* stats);
+
+}  // namespace efa

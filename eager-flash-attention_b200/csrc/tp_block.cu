@@ -1,0 +1,369 @@
+// Execution modes of the tensor-parallel attention block (attention -> projection -> sum AllReduce).
+// Counterpart of run_drivers.cu of eager-flash-attention (run_drivers.cu:9-30, 48-292): same seven
+// modes, same timing convention (barrier, host clock, enqueue, synchronise, max over ranks), same
+// stream roles; fp16 O / projection / reduction instead of fp32, and scratch cached in the context.
+#include "runtime.h"
+
+#include "fa_fwd_sm100.cuh"
+#include "host_util.h"
+#include "nccl_dyn.h"
+#include "p2p_reduce.h"
+
+#include <chrono>
+#include <cstring>
+#include <thread>
+
+namespace efa {
+
+namespace {
+
+const char* kModeNames[EFA_MODE_COUNT] = {"attn", "attn_tiled", "megatron", "sync", "overlap", "stream", "comm"};
+
+double now_ms()
+{
+    using namespace std::chrono;
+    return duration<double, std::milli>(steady_clock::now().time_since_epoch()).count();
+}
+
+struct Run {
+    efa_ctx* c;
+    const efa_weights& w;
+    const efa_params& p;
+    int launches = 0;
+
+    efa_flash_partials ws(int rows) const
+    {
+        efa_flash_partials q{c->ws_O, c->ws_m, c->ws_l, rows};
+        if (p.split <= 1) q = efa_flash_partials{nullptr, nullptr, nullptr, rows};
+        return q;
+    }
+
+    // Attention kernel only (launch_attention_raw, attn_main.cu:234-245).
+    int attention_raw(__half* O, int ws_rows, int q_start, int q_rows, cudaStream_t s, int* counters, int tile_rows)
+    {
+        efa_flash_partials q = ws(ws_rows);
+        launches++;
+        return fa_forward(w.Qh, w.Kh, w.Vh, O, EFA_F16, &q, q_start, q_rows, p.flash_tc, s, counters, tile_rows);
+    }
+    // launch_combine (attn_main.cu:247-252): no-op when split == 1.
+    int combine(__half* O, int ws_rows, int row0, int rows, cudaStream_t s)
+    {
+        if (p.split <= 1) return 0;
+        launches++;
+        return fa_combine(ws(ws_rows), O, EFA_F16, row0, rows, p.flash_tc, s);
+    }
+    int attention(__half* O, int ws_rows, int q_start, int q_rows, cudaStream_t s)
+    {
+        if (attention_raw(O, ws_rows, q_start, q_rows, s, nullptr, 0)) return 1;
+        return combine(O, ws_rows, 0, q_rows, s);
+    }
+    // project (attn_main.cu:262-273) on the projection stream.
+    int project(const __half* O_tile, __half* out, int rows)
+    {
+        if (p.skip_proj) return 0;
+        launches++;
+        return project_f16(O_tile, w.W_O, out, rows, p.d_local, p.d, c->proj_stream);
+    }
+    // allreduce (run_drivers.cu:26-30): communicator slot `slot`, fp16 sum.
+    int allreduce(int slot, const __half* send, __half* recv, size_t n)
+    {
+        if (p.skip_comm) return 0;
+        const NcclApi* nccl = nccl_api();
+        if (!nccl) return 1;
+        ncclResult_t r = nccl->AllReduce(send, recv, n, ncclHalf, ncclSum, c->nccls[slot], c->comm_streams[slot]);
+        if (r != ncclSuccess) { set_error("ncclAllReduce: %s", nccl->GetErrorString(r)); return 1; }
+        return 0;
+    }
+};
+
+// Wait for a stream with a deadline. When the deadline passes (a tile counter that never reaches
+// its target would block cuStreamWaitValue32 forever), the counters are overwritten with a large
+// value from another stream so that every pending wait is released, and an error is returned.
+int sync_stream(efa_ctx* c, cudaStream_t s, int* counters, size_t ncounters)
+{
+    const double deadline_ms = 120000.0;
+    const double t0 = now_ms();
+    long spins = 0;
+    while (true) {
+        cudaError_t e = cudaStreamQuery(s);
+        if (e == cudaSuccess) return 0;
+        if (e != cudaErrorNotReady) return check_cuda(e, "cudaStreamQuery", __FILE__, __LINE__);
+        if ((++spins & 1023) == 0) {
+            const double el = now_ms() - t0;
+            if (el > deadline_ms) break;
+            if (el > 2000.0) std::this_thread::sleep_for(std::chrono::microseconds(200));
+        }
+    }
+    if (counters && ncounters) {
+        cudaStream_t rescue;
+        if (cudaStreamCreateWithFlags(&rescue, cudaStreamNonBlocking) == cudaSuccess) {
+            cudaMemsetAsync(counters, 0x7f, ncounters * sizeof(int), rescue);
+            cudaStreamSynchronize(rescue);
+            cudaStreamDestroy(rescue);
+        }
+    }
+    set_error("stream did not finish within %.0f s; pending tile waits were released", deadline_ms / 1e3);
+    return 4;
+}
+
+int sync_comm_streams(efa_ctx* c)
+{
+    for (int i = 0; i < c->ncomm; i++)
+        if (sync_stream(c, c->comm_streams[i], nullptr, 0)) return 1;
+    return 0;
+}
+
+int finish_timing(efa_ctx* c, double t0, efa_run_stats* st, bool attn_events, bool proj_events, int launches)
+{
+    double ms = now_ms() - t0;
+    if (world_max(c->world, &ms)) return 1;
+    if (st) {
+        st->wall_ms = ms;
+        st->attn_kernel_ms = 0.f;
+        st->proj_ms = 0.f;
+        st->kernel_launches = launches;
+        if (attn_events) EFA_CUDA(cudaEventElapsedTime(&st->attn_kernel_ms, c->ev_t0, c->ev_t1));
+        if (proj_events) EFA_CUDA(cudaEventElapsedTime(&st->proj_ms, c->ev_t2, c->ev_t3));
+    }
+    return 0;
+}
+
+int scratch(efa_ctx* c, const efa_params& p, size_t o_rows, size_t send_rows, size_t ncounters, size_t ws_rows, size_t nevents)
+{
+    if (o_rows && ensure_bytes(&c->O_all, &c->O_all_bytes, o_rows * p.d_local * sizeof(__half))) return 1;
+    if (send_rows && ensure_bytes(&c->send_buf, &c->send_bytes, send_rows * p.d * sizeof(__half))) return 1;
+    if (ncounters) {
+        size_t have = c->counters_n * sizeof(int);
+        if (ensure_bytes((void**)&c->counters, &have, ncounters * sizeof(int))) return 1;
+        c->counters_n = have / sizeof(int);
+    }
+    if (p.split > 1 && ws_rows) {
+        size_t haveO = c->ws_O_n * sizeof(float);
+        if (ensure_bytes((void**)&c->ws_O, &haveO, (size_t)p.split * ws_rows * p.d_local * sizeof(float))) return 1;
+        c->ws_O_n = haveO / sizeof(float);
+        size_t want = (size_t)p.split * ws_rows * p.H_local * sizeof(float);
+        size_t haveM = c->ws_ml_n * sizeof(float), haveL = c->ws_ml_n * sizeof(float);
+        if (ensure_bytes((void**)&c->ws_m, &haveM, want)) return 1;
+        if (ensure_bytes((void**)&c->ws_l, &haveL, want)) return 1;
+        c->ws_ml_n = std::min(haveM, haveL) / sizeof(float);
+    }
+    if (nevents && ensure_events(c, nevents)) return 1;
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+
+// run_attn_only (run_drivers.cu:48-70)
+int run_attn_only(Run& r, efa_run_stats* st, bool tiled)
+{
+    efa_ctx* c = r.c; const efa_params& p = r.p;
+    if (scratch(c, p, p.S, 0, 0, tiled ? p.tile : p.S, 0)) return 1;
+    __half* O_all = static_cast<__half*>(c->O_all);
+    if (world_barrier(c->world)) return 1;
+    const double t0 = now_ms();
+    EFA_CUDA(cudaEventRecord(c->ev_t0, c->compute_stream));
+    if (tiled) {
+        for (int t = 0; t < p.num_tiles; t++)
+            if (r.attention(O_all + (size_t)t * p.tile * p.d_local, p.tile, t * p.tile, p.tile, c->compute_stream)) return 1;
+    } else {
+        if (r.attention(O_all, p.S, 0, p.S, c->compute_stream)) return 1;
+    }
+    EFA_CUDA(cudaEventRecord(c->ev_t1, c->compute_stream));
+    if (sync_stream(c, c->compute_stream, nullptr, 0)) return 1;
+    return finish_timing(c, t0, st, true, false, r.launches);
+}
+
+// run_megatron (run_drivers.cu:72-106)
+int run_megatron(Run& r, __half* output, efa_run_stats* st)
+{
+    efa_ctx* c = r.c; const efa_params& p = r.p;
+    if (scratch(c, p, p.S, p.S, 0, p.S, 2)) return 1;
+    __half* O_all = static_cast<__half*>(c->O_all);
+    __half* send_buf = static_cast<__half*>(c->send_buf);
+    cudaEvent_t attn_done = c->events[0], proj_done = c->events[1];
+
+    if (world_barrier(c->world)) return 1;
+    const double t0 = now_ms();
+    EFA_CUDA(cudaEventRecord(c->ev_t0, c->compute_stream));
+    if (r.attention(O_all, p.S, 0, p.S, c->compute_stream)) return 1;
+    EFA_CUDA(cudaEventRecord(c->ev_t1, c->compute_stream));
+    EFA_CUDA(cudaEventRecord(attn_done, c->compute_stream));
+
+    EFA_CUDA(cudaStreamWaitEvent(c->proj_stream, attn_done, 0));
+    EFA_CUDA(cudaEventRecord(c->ev_t2, c->proj_stream));
+    if (r.project(O_all, send_buf, p.S)) return 1;
+    EFA_CUDA(cudaEventRecord(c->ev_t3, c->proj_stream));
+    EFA_CUDA(cudaEventRecord(proj_done, c->proj_stream));
+
+    EFA_CUDA(cudaStreamWaitEvent(c->comm_streams[0], proj_done, 0));
+    if (r.allreduce(0, send_buf, output, (size_t)p.S * p.d)) return 1;
+    if (sync_stream(c, c->comm_streams[0], nullptr, 0)) return 1;
+    return finish_timing(c, t0, st, true, true, r.launches);
+}
+
+// run_sync (run_drivers.cu:108-136)
+int run_sync(Run& r, __half* output, efa_run_stats* st)
+{
+    efa_ctx* c = r.c; const efa_params& p = r.p;
+    if (scratch(c, p, p.tile, p.tile, 0, p.tile, 0)) return 1;
+    __half* O_tile = static_cast<__half*>(c->O_all);
+    __half* send_buf = static_cast<__half*>(c->send_buf);
+    if (world_barrier(c->world)) return 1;
+    const double t0 = now_ms();
+    for (int t = 0; t < p.num_tiles; t++) {
+        if (r.attention(O_tile, p.tile, t * p.tile, p.tile, c->compute_stream)) return 1;
+        if (sync_stream(c, c->compute_stream, nullptr, 0)) return 1;
+        if (r.project(O_tile, send_buf, p.tile)) return 1;
+        if (sync_stream(c, c->proj_stream, nullptr, 0)) return 1;
+        if (r.allreduce(0, send_buf, output + (size_t)t * p.tile * p.d, (size_t)p.tile * p.d)) return 1;
+        if (sync_stream(c, c->comm_streams[0], nullptr, 0)) return 1;
+    }
+    return finish_timing(c, t0, st, false, false, r.launches);
+}
+
+// run_overlap (run_drivers.cu:143-194): every tile enqueued up front, three streams ordered by events:
+//   compute: attn(t)  waits proj_done(t - nbuf)            (O buffer b free)
+//   proj:    gemm(t)  waits attn_done(t), comm_done(t - nbuf)   (send buffer b free)
+//   comm[t % ncomm]: allreduce(t) waits proj_done(t)
+int run_overlap(Run& r, __half* output, efa_run_stats* st)
+{
+    efa_ctx* c = r.c; const efa_params& p = r.p;
+    const int nbuf = p.nbuf;
+    if (scratch(c, p, (size_t)nbuf * p.tile, (size_t)nbuf * p.tile, 0, p.tile, (size_t)3 * nbuf)) return 1;
+    __half* O_buf = static_cast<__half*>(c->O_all);
+    __half* S_buf = static_cast<__half*>(c->send_buf);
+    auto attn_done = [&](int b) { return c->events[3 * b]; };
+    auto proj_done = [&](int b) { return c->events[3 * b + 1]; };
+    auto comm_done = [&](int b) { return c->events[3 * b + 2]; };
+
+    if (world_barrier(c->world)) return 1;
+    const double t0 = now_ms();
+    for (int t = 0; t < p.num_tiles; t++) {
+        const int b = t % nbuf;
+        __half* O_t = O_buf + (size_t)b * p.tile * p.d_local;
+        __half* S_t = S_buf + (size_t)b * p.tile * p.d;
+        if (t >= nbuf) EFA_CUDA(cudaStreamWaitEvent(c->compute_stream, proj_done(b), 0));
+        if (r.attention(O_t, p.tile, t * p.tile, p.tile, c->compute_stream)) return 1;
+        EFA_CUDA(cudaEventRecord(attn_done(b), c->compute_stream));
+
+        EFA_CUDA(cudaStreamWaitEvent(c->proj_stream, attn_done(b), 0));
+        if (t >= nbuf) EFA_CUDA(cudaStreamWaitEvent(c->proj_stream, comm_done(b), 0));
+        if (r.project(O_t, S_t, p.tile)) return 1;
+        EFA_CUDA(cudaEventRecord(proj_done(b), c->proj_stream));
+
+        const int slot = t % c->ncomm;
+        EFA_CUDA(cudaStreamWaitEvent(c->comm_streams[slot], proj_done(b), 0));
+        if (r.allreduce(slot, S_t, output + (size_t)t * p.tile * p.d, (size_t)p.tile * p.d)) return 1;
+        EFA_CUDA(cudaEventRecord(comm_done(b), c->comm_streams[slot]));
+    }
+    if (sync_stream(c, c->compute_stream, nullptr, 0)) return 1;
+    if (sync_stream(c, c->proj_stream, nullptr, 0)) return 1;
+    if (sync_comm_streams(c)) return 1;
+    return finish_timing(c, t0, st, false, false, r.launches);
+}
+
+// run_stream (run_drivers.cu:201-255): one attention launch over all rows; the kernel counts finished
+// 64-row blocks per tile; the projection stream holds, for every tile, a front-end wait on that
+// tile's counter (cuStreamWaitValue32, no SM involved), the split combine, the projection and an
+// event; the tile's AllReduce follows on communicator t % ncomm.
+int run_stream(Run& r, __half* output, efa_run_stats* st)
+{
+    efa_ctx* c = r.c; const efa_params& p = r.p;
+    const DriverApi* api = driver_api();
+    if (!api) return 1;
+    if (scratch(c, p, p.S, p.S, p.num_tiles, p.S, (size_t)p.num_tiles + 1)) return 1;
+    __half* O_all = static_cast<__half*>(c->O_all);
+    __half* send_buf = static_cast<__half*>(c->send_buf);
+    int* counters = c->counters;
+    const int target = efa_blocks_per_tile(&p);
+    cudaEvent_t reset_done = c->events[p.num_tiles];
+    const bool fused = (p.reduce == EFA_REDUCE_P2P) && !p.skip_comm && !p.skip_proj;
+    if (fused && p2p_prepare(c, p, output)) return 1;
+
+    if (world_barrier(c->world)) return 1;
+    const double t0 = now_ms();
+
+    EFA_CUDA(cudaMemsetAsync(counters, 0, (size_t)p.num_tiles * sizeof(int), c->compute_stream));
+    EFA_CUDA(cudaEventRecord(reset_done, c->compute_stream));
+    EFA_CUDA(cudaEventRecord(c->ev_t0, c->compute_stream));
+    if (r.attention_raw(O_all, p.S, 0, p.S, c->compute_stream, counters, p.tile)) return 1;
+    EFA_CUDA(cudaEventRecord(c->ev_t1, c->compute_stream));
+
+    EFA_CUDA(cudaStreamWaitEvent(c->proj_stream, reset_done, 0));   // never observe a stale counter
+    for (int t = 0; t < p.num_tiles; t++) {
+        EFA_CU(api->cuStreamWaitValue32((CUstream)c->proj_stream, (CUdeviceptr)(counters + t),
+                                        (cuuint32_t)target, CU_STREAM_WAIT_VALUE_GEQ));
+        __half* O_t = O_all + (size_t)t * p.tile * p.d_local;
+        __half* S_t = send_buf + (size_t)t * p.tile * p.d;
+        if (r.combine(O_t, p.S, t * p.tile, p.tile, c->proj_stream)) return 1;
+        if (fused) {
+            if (p2p_tile(c, p, r.w, O_t, t, &r.launches)) return 1;
+            continue;
+        }
+        if (r.project(O_t, S_t, p.tile)) return 1;
+        EFA_CUDA(cudaEventRecord(c->events[t], c->proj_stream));
+        const int slot = t % c->ncomm;
+        EFA_CUDA(cudaStreamWaitEvent(c->comm_streams[slot], c->events[t], 0));
+        if (r.allreduce(slot, S_t, output + (size_t)t * p.tile * p.d, (size_t)p.tile * p.d)) return 1;
+    }
+    if (fused && p2p_finish(c, p)) return 1;
+    if (sync_stream(c, c->compute_stream, counters, p.num_tiles)) return 1;
+    if (sync_stream(c, c->proj_stream, counters, p.num_tiles)) return 1;
+    if (sync_comm_streams(c)) return 1;
+    return finish_timing(c, t0, st, true, false, r.launches);
+}
+
+// run_comm_only (run_drivers.cu:259-275): the per-tile AllReduces of a full pass, back to back on
+// communicator 0; sweeping the tile size gives t_allreduce(bytes).
+int run_comm_only(Run& r, __half* output, efa_run_stats* st)
+{
+    efa_ctx* c = r.c; const efa_params& p = r.p;
+    if (scratch(c, p, 0, p.S, 0, 0, 0)) return 1;
+    __half* send_buf = static_cast<__half*>(c->send_buf);
+    EFA_CUDA(cudaMemset(send_buf, 0, (size_t)p.S * p.d * sizeof(__half)));
+    if (world_barrier(c->world)) return 1;
+    const double t0 = now_ms();
+    for (int t = 0; t < p.num_tiles; t++)
+        if (r.allreduce(0, send_buf + (size_t)t * p.tile * p.d, output + (size_t)t * p.tile * p.d, (size_t)p.tile * p.d)) return 1;
+    if (sync_stream(c, c->comm_streams[0], nullptr, 0)) return 1;
+    return finish_timing(c, t0, st, false, false, r.launches);
+}
+
+}  // namespace
+
+int run_mode_impl(efa_ctx* c, int mode, const efa_weights& w, void* output, const efa_params& p, efa_run_stats* stats)
+{
+    if (!c) { set_error("run_mode: null context"); return 2; }
+    if (const char* why = efa_attn_check_params(&p)) { set_error("invalid params: %s", why); return 2; }
+    if (p.R != c->world.size) { set_error("params are for %d ranks, the context has %d", p.R, c->world.size); return 2; }
+    if (!w.Qh || !w.Kh || !w.Vh || !w.W_O) { set_error("run_mode: null weights"); return 2; }
+    if (mode != EFA_MODE_ATTN && mode != EFA_MODE_ATTN_TILED && !output) { set_error("run_mode: null output"); return 2; }
+    Run r{c, w, p};
+    __half* out = static_cast<__half*>(output);
+    switch (mode) {
+        case EFA_MODE_ATTN:       return run_attn_only(r, stats, false);
+        case EFA_MODE_ATTN_TILED: return run_attn_only(r, stats, true);
+        case EFA_MODE_MEGATRON:   return run_megatron(r, out, stats);
+        case EFA_MODE_SYNC:       return run_sync(r, out, stats);
+        case EFA_MODE_OVERLAP:    return run_overlap(r, out, stats);
+        case EFA_MODE_STREAM:     return run_stream(r, out, stats);
+        case EFA_MODE_COMM:       return run_comm_only(r, out, stats);
+    }
+    set_error("unknown mode %d", mode);
+    return 2;
+}
+
+}  // namespace efa
+
+extern "C" const char* efa_mode_name(int mode)
+{
+    return (mode >= 0 && mode < EFA_MODE_COUNT) ? efa::kModeNames[mode] : "?";
+}
+
+extern "C" int efa_parse_mode(const char* s)
+{
+    if (!s) return -1;
+    for (int i = 0; i < EFA_MODE_COUNT; i++)
+        if (std::strcmp(s, efa::kModeNames[i]) == 0) return i;
+    return -1;
+}

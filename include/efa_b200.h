@@ -1,0 +1,194 @@
+/* C ABI of the B200 (sm_100a) tensor-parallel attention block.
+ *
+ * The block is: head-sharded FlashAttention -> per-rank output projection -> sum AllReduce, with the
+ * projection and reduction of each finished row tile started while attention is still running.
+ * Every entry point takes plain pointers and sizes. Device pointers are CUDA device pointers of
+ * the current device; `stream` arguments are cudaStream_t handles passed as void*.
+ *
+ * Unless stated otherwise a function returns 0 on success and a non-zero code on failure, in
+ * which case efa_last_error() describes the failure (per thread). Nothing in this library falls
+ * back to host arithmetic: without a usable sm_100 device the compute entry points fail.
+ *
+ * Each declaration cites the interface of eager-flash-attention (file:line within that project)
+ * that it stands in for.
+ */
+#ifndef EFA_B200_H
+#define EFA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define EFA_ABI_VERSION 1
+
+/* Element types of O / output buffers. */
+#define EFA_F32 0
+#define EFA_F16 1
+
+int         efa_abi_version(void);
+const char* efa_last_error(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Kernel launch interface
+ * ------------------------------------------------------------------------------------------ */
+
+/* Same fields, order and meaning as FlashAttnTCParams (flash_attn_tc.cuh:16-23). */
+typedef struct efa_flash_params {
+    int   S;
+    int   d_h;      /* 16, 32, 64 or 128 */
+    int   H_local;
+    int   split;    /* split-KV factor (1 = off) */
+    int   causal;
+    float scale;    /* softmax scale, 1/sqrt(d_h) */
+} efa_flash_params;
+
+/* Same fields, order and meaning as FlashAttnTCPartials (flash_attn_tc.cuh:25-34):
+ *   O_part [split][rows][H_local*d_h] unnormalised, m_part / l_part [split][rows][H_local],
+ *   row max in the log2 domain and row denominator. */
+typedef struct efa_flash_partials {
+    float* O_part;
+    float* m_part;
+    float* l_part;
+    int    rows;
+} efa_flash_partials;
+
+/* flash_attn_tc_forward (flash_attn_tc.cuh:45-50; kernel flash_attn_tc.cu:73-312).
+ * Q, K, V: fp16 [H_local][S][d_h]. O: [q_rows][H_local*d_h], fp32 (EFA_F32, the reference's type)
+ * or fp16 (EFA_F16, what the projection kernel consumes). Rows q_start .. q_start+q_rows.
+ * With split > 1 the partials go to `part` and O is untouched until efa_flash_attn_tc_combine.
+ * If tile_counters != NULL, tile_counters[(row within launch)/tile_rows] is incremented once per
+ * finished 64-row block per (head, split) after that block's rows are visible device-wide
+ * (__threadfence + atomicAdd, flash_attn_tc.cu:305-311). Asynchronous on `stream`. */
+int efa_flash_attn_tc_forward(const void* Q, const void* K, const void* V,
+                              void* O, int o_dtype, const efa_flash_partials* part,
+                              int q_start, int q_rows, const efa_flash_params* p, void* stream,
+                              int* tile_counters, int tile_rows);
+
+/* flash_attn_tc_combine (flash_attn_tc.cuh:54-57; kernel flash_attn_tc.cu:319-361): merge the
+ * split partials of workspace rows [row0, row0+rows) into O[0..rows). */
+int efa_flash_attn_tc_combine(const efa_flash_partials* part, void* O, int o_dtype,
+                              int row0, int rows, const efa_flash_params* p, void* stream);
+
+/* flash_attn_tc_check_params (flash_attn_tc.cuh:59-60, flash_attn_tc.cu:401-409):
+ * NULL when the launch is legal, else a static description. */
+const char* efa_flash_attn_tc_check_params(const efa_flash_params* p, int q_rows);
+
+/* convert_f32_to_f16 (flash_attn_tc.cuh:62, flash_attn_tc.cu:411-424), round to nearest even. */
+int efa_convert_f32_to_f16(const float* in, void* out, size_t n, void* stream);
+
+/* project (attn_main.cuh:62-65, attn_main.cu:262-273) for the fp16 data path:
+ * out[rows][d] = O_tile[rows][d_local] * W_O[d_local][d], fp16 operands, fp32 accumulate, fp16 out.
+ * rows must be a multiple of 64, d_local a multiple of 16, d a multiple of 64. */
+int efa_project_f16(const void* O_tile, const void* W_O, void* out,
+                    int rows, int d_local, int d, void* stream);
+
+/* Status word written by kernels whose bounded waits ran out: out4 = {code, block, site, 0};
+ * code 0 = no kernel reported a problem since the last efa_kernel_status_reset(). */
+int efa_kernel_status(int* out4);
+int efa_kernel_status_reset(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Runtime interface
+ * ------------------------------------------------------------------------------------------ */
+
+/* Execution modes, same numbering and names as RunMode (run_drivers.cuh:6-17, run_drivers.cu:9-11). */
+enum {
+    EFA_MODE_ATTN = 0, EFA_MODE_ATTN_TILED = 1, EFA_MODE_MEGATRON = 2, EFA_MODE_SYNC = 3,
+    EFA_MODE_OVERLAP = 4, EFA_MODE_STREAM = 5, EFA_MODE_COMM = 6, EFA_MODE_COUNT = 7
+};
+const char* efa_mode_name(int mode);     /* mode_name  (run_drivers.cuh:19) */
+int         efa_parse_mode(const char* s); /* parse_mode (run_drivers.cuh:20), -1 if unknown */
+
+/* How the per-tile partial sums are reduced across ranks. */
+enum { EFA_REDUCE_NCCL = 0, EFA_REDUCE_P2P = 1 };
+
+/* Derived problem description: AttnParams (attn_defs.cuh:70-84) without the fields of the
+ * removed legacy kernel (B_M, B_N, kernel, flash). */
+typedef struct efa_params {
+    int S, d, H, R;
+    int H_local, d_h, d_local;
+    int tile, num_tiles;
+    int nbuf, split, causal;
+    int skip_proj, skip_comm;
+    int reduce;                 /* EFA_REDUCE_* */
+    efa_flash_params flash_tc;
+} efa_params;
+
+/* make_params (attn_main.cuh:18-19, attn_main.cu:35-60). */
+int efa_make_params(efa_params* out, int S, int d, int H, int tile, int nbuf, int split, int causal, int world_size);
+/* attn_check_params (attn_main.cuh:22, attn_main.cu:62-74): NULL if runnable. */
+const char* efa_attn_check_params(const efa_params* p);
+/* blocks_per_tile (attn_main.cuh:68, attn_main.cu:275-280): the counter target of a tile. */
+int efa_blocks_per_tile(const efa_params* p);
+
+/* Host control plane of one rank. The reference uses MPI for exactly these four operations
+ * (MPI_Barrier / MPI_Allreduce(MAX) / MPI_Bcast / and, new here, an all-gather of opaque bytes for
+ * IPC handles); a caller supplies them over whatever it has (the bundled shared-memory shim, or
+ * torch.distributed). Callbacks return 0 on success. With size == 1 they may be NULL. */
+typedef struct efa_world {
+    void* user;
+    int   rank, size;
+    int   local_device;   /* CUDA device ordinal of this rank */
+    int (*barrier)(void* user);
+    int (*allreduce_max_f64)(void* user, double* value);
+    int (*bcast_bytes)(void* user, void* buf, size_t n, int root);
+    int (*allgather_bytes)(void* user, const void* in, void* out, size_t n_each);
+} efa_world;
+
+/* Runs each callback of a world once (barrier, max, broadcast, all-gather) and checks that the
+ * results agree with rank and size. Host only, no CUDA call. The reference has no counterpart: it
+ * is a set-up check for callers that bring their own control plane in place of MPI
+ * (MPI_Barrier / MPI_Allreduce / MPI_Bcast at run_drivers.cu:38-44, attn_main.cu:155-163). */
+int efa_world_selftest(const efa_world* world);
+
+typedef struct efa_ctx efa_ctx;   /* RunCtx (attn_defs.cuh:86-99): streams, communicators */
+
+/* make_ctx / destroy_ctx (attn_main.cuh:43-44, attn_main.cu:180-213): one compute stream (lowest
+ * priority), one projection stream and ncomm communication streams (highest priority when
+ * `prioritize`), ncomm NCCL communicators over the world's ranks. Collective over the world. */
+int efa_make_ctx(efa_ctx** out, const efa_world* world, int ncomm, int prioritize);
+int efa_destroy_ctx(efa_ctx* ctx);
+
+/* Device tensors of one rank: Weights (attn_main.cuh:7-12) for the fp16 data path. */
+typedef struct efa_weights {
+    void* Qh; void* Kh; void* Vh;   /* fp16 [H_local][S][d_h] */
+    void* W_O;                      /* fp16 [d_local][d] */
+} efa_weights;
+
+/* Synthetic inputs on the HOST (fp16 bit patterns), written into caller-provided buffers:
+ *   recipe 0 ("ref"):    allocate_and_fill + compute_qkv (attn_main.cu:88-153): glibc rand(),
+ *                        X = U(-1,1) seeded `seed`, weights seeded seed*31+rank+1, Q/K/V = X*W in
+ *                        fp32 then rounded to fp16; W_O rounded to fp16.
+ *   recipe 1 ("normal"): Q, K, V ~ N(0,1), W_O ~ N(0, 1/d), keyed by (seed, tensor, global head, row,
+ *                        column) so that every rank count yields the same global tensors.
+ * Sizes: Q/K/V H_local*S*d_h halves each, W_O d_local*d halves. */
+int efa_fill_host_inputs(const efa_params* p, int rank, int seed, int recipe,
+                         uint16_t* Qh, uint16_t* Kh, uint16_t* Vh, uint16_t* W_O);
+
+/* Timing record of one efa_run_mode call. */
+typedef struct efa_run_stats {
+    double wall_ms;        /* barrier -> enqueue -> sync, max over ranks (run_drivers.cu:38-44) */
+    float  attn_kernel_ms; /* CUDA-event time of the attention kernel on the compute stream, this rank */
+    float  proj_ms;        /* CUDA-event time of the projection kernel (megatron mode), this rank, else 0 */
+    int    kernel_launches;/* kernels of this library launched inside the timed region, this rank */
+} efa_run_stats;
+
+/* run_mode (run_drivers.cuh:22-26, run_drivers.cu:277-292). `output`: fp16 [S][d] device buffer,
+ * the reduced result, identical on every rank (untouched by attn / attn_tiled). Collective. */
+int efa_run_mode(efa_ctx* ctx, int mode, const efa_weights* w, void* output,
+                 const efa_params* p, efa_run_stats* stats);
+
+/* The whole block on HOST buffers: copies this rank's fp16 Q/K/V/W_O to the device, runs `mode`,
+ * copies the fp16 [S][d] result back. The copies are inside wall_ms. Buffers should be pinned.
+ * Device staging is allocated on the first call for a given shape and reused. */
+int efa_run_mode_host(efa_ctx* ctx, int mode,
+                      const uint16_t* Qh, const uint16_t* Kh, const uint16_t* Vh, const uint16_t* W_O,
+                      uint16_t* output, const efa_params* p, efa_run_stats* stats);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* EFA_B200_H */

@@ -1,0 +1,107 @@
+"""Every execution mode that writes an output (megatron, sync, overlap, stream) against the CPU checker:
+the reference's test matrix (attn_tests.cu:70-87, 124-139) on one rank, plus the single-GPU
+configuration of the benchmark plan (S=4096, H=16, d_h=64, tile=128, N(0,1) inputs)."""
+import numpy as np
+import pytest
+
+from conftest import REFERENCE_CASES, REFERENCE_SEEDS
+from helpers import assert_close, normal_inputs_f16, ref_inputs_f16, to_dev
+
+pytestmark = pytest.mark.gpu
+
+CHECKED_MODES = ("megatron", "sync", "overlap", "stream")
+
+
+@pytest.fixture(scope="module")
+def ctx(pkg, torch_cuda):
+    c = pkg.make_ctx(pkg.World(), ncomm=3)       # the reference's tests use three communicators
+    yield c
+    pkg.destroy_ctx(c)
+
+
+@pytest.mark.parametrize("case", REFERENCE_CASES, ids=lambda c: "S%d_d%d_H%d_t%d_n%d_s%d_c%d" % c)
+def test_reference_matrix_single_rank(pkg, oracle, torch_cuda, ctx, case):
+    torch = torch_cuda
+    S, d, H, tile, nbuf, split, causal = case
+    p = pkg.make_params(S, d, H, tile, nbuf, split, causal)
+    assert pkg.attn_check_params(p) is None
+    seeds = REFERENCE_SEEDS if S <= 512 else REFERENCE_SEEDS[:1]
+    for seed in seeds:
+        bits, vals = ref_inputs_f16(oracle, S, d, H, 1, 0, seed)
+        ref = oracle.block_rows([vals], d, causal)
+        dev = to_dev(torch, bits)
+        w = pkg.Weights(*(t.data_ptr() for t in dev))
+        for name in CHECKED_MODES:
+            out = torch.full((S, d), float("nan"), dtype=torch.float16, device="cuda")
+            pkg.kernel_status_reset()
+            st = pkg.run_mode(ctx, pkg.parse_mode(name), w, out, p)
+            torch.cuda.synchronize()
+            assert pkg.kernel_status()[0] == 0
+            assert st.wall_ms > 0 and st.kernel_launches > 0
+            assert_close(oracle, out.float().cpu().numpy(), ref, f"{name} seed {seed}")
+
+
+def test_attention_only_modes_leave_output_untouched(pkg, oracle, torch_cuda, ctx):
+    torch = torch_cuda
+    S, d, H, tile = 512, 256, 4, 128
+    p = pkg.make_params(S, d, H, tile)
+    bits, _ = ref_inputs_f16(oracle, S, d, H, 1, 0, 42)
+    dev = to_dev(torch, bits)
+    w = pkg.Weights(*(t.data_ptr() for t in dev))
+    out = torch.full((S, d), 7.0, dtype=torch.float16, device="cuda")
+    for name in ("attn", "attn_tiled"):
+        st = pkg.run_mode(ctx, pkg.parse_mode(name), w, out, p)
+        assert st.attn_kernel_ms > 0
+    torch.cuda.synchronize()
+    assert bool((out == 7.0).all())
+
+
+def test_diagnostic_flags_skip_stages(pkg, oracle, torch_cuda, ctx):
+    """--no_proj / --no_comm (attn_bench.cu:120-121): the run completes and launches fewer kernels."""
+    torch = torch_cuda
+    S, d, H, tile = 512, 256, 4, 128
+    p = pkg.make_params(S, d, H, tile)
+    bits, _ = ref_inputs_f16(oracle, S, d, H, 1, 0, 42)
+    dev = to_dev(torch, bits)
+    w = pkg.Weights(*(t.data_ptr() for t in dev))
+    out = torch.zeros((S, d), dtype=torch.float16, device="cuda")
+    full = pkg.run_mode(ctx, pkg.MODE_STREAM, w, out, p).kernel_launches
+    p.skip_proj = 1
+    assert pkg.run_mode(ctx, pkg.MODE_STREAM, w, out, p).kernel_launches == full - p.num_tiles
+    p.skip_proj, p.skip_comm = 0, 1
+    assert pkg.run_mode(ctx, pkg.MODE_STREAM, w, out, p).kernel_launches == full
+
+
+@pytest.mark.parametrize("causal", [0, 1])
+def test_single_gpu_benchmark_configuration(pkg, oracle, torch_cuda, ctx, causal):
+    """S=4096, H=16, d_h=64, D=1024, tile=128, N(0,1) Q/K/V, W_O ~ N(0, 1/1024); modes attn, megatron,
+    stream; checked on a fixed sample of rows from the first, last and interior tiles."""
+    torch = torch_cuda
+    S, d, H, tile = 4096, 1024, 16, 128
+    p = pkg.make_params(S, d, H, tile, causal=causal)
+    bits, vals = normal_inputs_f16(pkg, oracle, p, 0, 42)
+    rng = np.random.default_rng(5)
+    rows = np.unique(np.concatenate([np.arange(0, 64), np.arange(S - 64, S), rng.integers(64, S - 64, 128)])).astype(np.int32)
+    ref = oracle.block_rows([vals], d, causal, rows)
+    dev = to_dev(torch, bits)
+    w = pkg.Weights(*(t.data_ptr() for t in dev))
+    for name in ("megatron", "stream"):
+        out = torch.full((S, d), float("nan"), dtype=torch.float16, device="cuda")
+        pkg.run_mode(ctx, pkg.parse_mode(name), w, out, p)
+        torch.cuda.synchronize()
+        got = out.float().cpu().numpy()
+        assert np.isfinite(got).all()
+        assert_close(oracle, got[rows], ref, name)
+
+
+def test_host_buffer_entry_point(pkg, oracle, torch_cuda, ctx):
+    torch = torch_cuda
+    S, d, H, tile = 512, 256, 4, 128
+    p = pkg.make_params(S, d, H, tile, causal=1)
+    bits, vals = ref_inputs_f16(oracle, S, d, H, 1, 0, 123)
+    ref = oracle.block_rows([vals], d, 1)
+    pinned = [torch.from_numpy(b.view(np.float16)).pin_memory() for b in bits]
+    out = torch.zeros((S, d), dtype=torch.float16).pin_memory()
+    st = pkg.run_mode_host(ctx, pkg.MODE_STREAM, *pinned, out, p)
+    assert st.wall_ms > 0
+    assert_close(oracle, out.float().numpy(), ref)
