@@ -83,6 +83,8 @@ _SIGNATURES = {
     "efa_flash_attn_tc_forward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int,
                                             C.POINTER(FlashPartials), C.c_int, C.c_int,
                                             C.POINTER(FlashParams), C.c_void_p, C.c_void_p, C.c_int]),
+    "efa_flash_attn_tc_forward_noalloc": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int,
+                                                    C.c_int, C.c_int, C.POINTER(FlashParams), C.c_void_p]),
     "efa_flash_attn_tc_combine": (C.c_int, [C.POINTER(FlashPartials), C.c_void_p, C.c_int, C.c_int, C.c_int,
                                             C.POINTER(FlashParams), C.c_void_p]),
     "efa_flash_attn_tc_check_params": (C.c_char_p, [C.POINTER(FlashParams), C.c_int]),
@@ -202,6 +204,21 @@ def flash_attn_tc_forward(Q, K, V, O, part: Optional[FlashPartials], q_start: in
                                          q_start, q_rows, C.byref(fp), _stream(stream),
                                          _ptr(tile_counters), tile_rows)
     _check(rc, "flash_attn_tc_forward")
+
+
+STATIC_SCRATCH_BYTES = 8 << 20
+
+
+def flash_attn_tc_forward_noalloc(Q, K, V, O, q_start: int, q_rows: int, fp: FlashParams, stream=None,
+                                  o_dtype: int = F16) -> None:
+    """Split-KV attention and merge in one call, for callers that cannot allocate device memory when
+    they call (a memory pool owns the GPU, or an allocation's device-wide synchronisation is not
+    acceptable): the partials live in a fixed STATIC_SCRATCH_BYTES array inside the library. Shapes
+    whose partials do not fit are rejected. Calls share that array, so do not let two overlap on the
+    GPU; make the first call on a device outside stream capture."""
+    rc = lib().efa_flash_attn_tc_forward_noalloc(_ptr(Q), _ptr(K), _ptr(V), _ptr(O), o_dtype, q_start, q_rows,
+                                                 C.byref(fp), _stream(stream))
+    _check(rc, "flash_attn_tc_forward_noalloc")
 
 
 def flash_attn_tc_combine(part: FlashPartials, O, row0: int, rows: int, fp: FlashParams, stream=None,

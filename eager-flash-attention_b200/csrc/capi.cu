@@ -20,6 +20,14 @@ extern "C" int efa_flash_attn_tc_forward(const void* Q, const void* K, const voi
     return fa_forward(Q, K, V, O, o_dtype, part, q_start, q_rows, *p, (cudaStream_t)stream, tile_counters, tile_rows);
 }
 
+extern "C" int efa_flash_attn_tc_forward_noalloc(const void* Q, const void* K, const void* V,
+                                                 void* O, int o_dtype, int q_start, int q_rows,
+                                                 const efa_flash_params* p, void* stream)
+{
+    if (!Q || !K || !V || !p) { set_error("efa_flash_attn_tc_forward_noalloc: null argument"); return 2; }
+    return fa_forward_noalloc(Q, K, V, O, o_dtype, q_start, q_rows, *p, (cudaStream_t)stream);
+}
+
 extern "C" int efa_flash_attn_tc_combine(const efa_flash_partials* part, void* O, int o_dtype,
                                          int row0, int rows, const efa_flash_params* p, void* stream)
 {

@@ -531,3 +531,105 @@ int convert_f32_to_f16_dev(const float* in, void* out, size_t n, cudaStream_t st
 }
 
 }  // namespace efa
+
+// ---------------------------------------------------------------------------------------------
+// Split-KV attention without any allocation by the caller or by this library
+// ---------------------------------------------------------------------------------------------
+// The split-KV path needs scratch for the per-split partial results. Normally the caller owns it
+// (efa_flash_partials). Some callers cannot obtain device memory at call time: a serving process
+// whose memory pool already holds the whole GPU, so that a plain cudaMalloc fails, or a
+// latency-critical loop that cannot afford the device-wide synchronisation cudaMalloc implies.
+// For them the partials live in the fixed array below, which is part of the loaded module: every
+// GPU that loads this library holds EFA_STATIC_SCRATCH_BYTES of it until the process exits.
+namespace efa {
+namespace {
+
+static __device__ __align__(256) float g_static_scratch[EFA_STATIC_SCRATCH_BYTES / sizeof(float)];
+
+// In host code `g_static_scratch` is only a handle for the symbol, not a device address: the address
+// that kernels may use comes from cudaGetSymbolAddress, once per device, with that device current.
+int static_scratch_address(float** out)
+{
+    static float* addr[64] = {};
+    static std::mutex mu;
+    int dev = 0;
+    EFA_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) { set_error("device ordinal %d out of range", dev); return 1; }
+    std::lock_guard<std::mutex> lock(mu);
+    if (!addr[dev]) {
+        void* p = nullptr;
+        EFA_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+        if (!p) { set_error("cudaGetSymbolAddress returned a null address for the static scratch"); return 1; }
+        addr[dev] = static_cast<float*>(p);
+    }
+    *out = addr[dev];
+    return 0;
+}
+
+int encode_qkv_tmap_uncached(const void* ptr, int S, int H_local, int D, CUtensorMap* out)
+{
+    const int boxc = D >= 64 ? 64 : D;
+    unsigned long long dims[3] = {(unsigned long long)D, (unsigned long long)S, (unsigned long long)H_local};
+    unsigned long long strides[2] = {(unsigned long long)D * 2ull, (unsigned long long)S * D * 2ull};
+    unsigned box[3] = {(unsigned)boxc, 128u, 1u};
+    return make_tmap_f16(out, ptr, 3, dims, strides, box);
+}
+
+}  // namespace
+
+int fa_forward_noalloc(const void* Q, const void* K, const void* V, void* O, int o_dtype,
+                       int q_start, int q_rows, const efa_flash_params& p, cudaStream_t stream)
+{
+    if (const char* why = fa_check_params(p, q_rows)) { set_error("flash_attn_tc_forward_noalloc: %s", why); return 2; }
+    if (q_start < 0 || q_start % 64 != 0 || q_start + q_rows > p.S) {
+        set_error("flash_attn_tc_forward_noalloc: rows [%d, %d) outside [0, %d) or not 64-aligned", q_start, q_start + q_rows, p.S);
+        return 2;
+    }
+    if (o_dtype != EFA_F32 && o_dtype != EFA_F16) { set_error("flash_attn_tc_forward_noalloc: unknown O dtype %d", o_dtype); return 2; }
+    if (!O) { set_error("flash_attn_tc_forward_noalloc: O is null"); return 2; }
+
+    const size_t d_local = (size_t)p.H_local * p.d_h;
+    const size_t o_floats = (size_t)p.split * q_rows * d_local;
+    const size_t ml_floats = (size_t)p.split * q_rows * p.H_local;
+    const size_t need = p.split > 1 ? (o_floats + 2 * ml_floats) * sizeof(float) : 0;
+    if (need > (size_t)EFA_STATIC_SCRATCH_BYTES) {
+        set_error("flash_attn_tc_forward_noalloc: split=%d rows=%d d_local=%zu needs %zu bytes of scratch, the static "
+                  "scratch holds %u; use efa_flash_attn_tc_forward with a caller-owned workspace",
+                  p.split, q_rows, d_local, need, (unsigned)EFA_STATIC_SCRATCH_BYTES);
+        return 6;
+    }
+    float* scratch = nullptr;
+    if (static_scratch_address(&scratch)) return 1;
+
+    CUtensorMap tq, tk, tv;
+    if (encode_qkv_tmap_uncached(Q, p.S, p.H_local, p.d_h, &tq) || encode_qkv_tmap_uncached(K, p.S, p.H_local, p.d_h, &tk) ||
+        encode_qkv_tmap_uncached(V, p.S, p.H_local, p.d_h, &tv))
+        return 1;
+
+    // Every partial that the combine step reads is written by the attention kernel earlier in the
+    // same call (idle blocks write zeros and an empty maximum), so nothing has to be cleared.
+    efa_flash_partials part{scratch, scratch + o_floats, scratch + o_floats + ml_floats, q_rows};
+    FaArgs a;
+    a.O32 = (o_dtype == EFA_F32) ? static_cast<float*>(O) : nullptr;
+    a.O16 = (o_dtype == EFA_F16) ? static_cast<__half*>(O) : nullptr;
+    a.O_part = part.O_part; a.m_part = part.m_part; a.l_part = part.l_part; a.part_rows = q_rows;
+    a.q_start = q_start; a.q_rows = q_rows; a.S = p.S; a.H_local = p.H_local;
+    a.nsplit = p.split; a.kv_len = p.S / p.split; a.causal = p.causal;
+    a.scale_log2e = p.scale * 1.4426950408889634f;
+    a.tile_counters = nullptr; a.tile_rows = 0;
+    a.status = nullptr;                      // the status word of the other entry points is allocated memory
+
+    dim3 grid(p.H_local * p.split, (q_rows + FA_BM - 1) / FA_BM);
+    const bool f16 = (o_dtype == EFA_F16);
+    int rc = 2;
+    switch (p.d_h) {
+        case 16:  rc = f16 ? launch_fa<16, true>(tq, tk, tv, a, grid, stream)  : launch_fa<16, false>(tq, tk, tv, a, grid, stream); break;
+        case 32:  rc = f16 ? launch_fa<32, true>(tq, tk, tv, a, grid, stream)  : launch_fa<32, false>(tq, tk, tv, a, grid, stream); break;
+        case 64:  rc = f16 ? launch_fa<64, true>(tq, tk, tv, a, grid, stream)  : launch_fa<64, false>(tq, tk, tv, a, grid, stream); break;
+        case 128: rc = f16 ? launch_fa<128, true>(tq, tk, tv, a, grid, stream) : launch_fa<128, false>(tq, tk, tv, a, grid, stream); break;
+    }
+    if (rc) return rc;
+    return fa_combine(part, O, o_dtype, 0, q_rows, p, stream);
+}
+
+}  // namespace efa

@@ -12,6 +12,10 @@ int fa_forward(const void* Q, const void* K, const void* V, void* O, int o_dtype
                const efa_flash_partials* part, int q_start, int q_rows,
                const efa_flash_params& p, cudaStream_t stream, int* tile_counters, int tile_rows);
 
+// Split-KV attention + merge with the partials in a fixed device array (no allocation anywhere).
+int fa_forward_noalloc(const void* Q, const void* K, const void* V, void* O, int o_dtype,
+                       int q_start, int q_rows, const efa_flash_params& p, cudaStream_t stream);
+
 int fa_combine(const efa_flash_partials& part, void* O, int o_dtype, int row0, int rows,
                const efa_flash_params& p, cudaStream_t stream);
 

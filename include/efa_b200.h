@@ -72,6 +72,29 @@ int efa_flash_attn_tc_forward(const void* Q, const void* K, const void* V,
 int efa_flash_attn_tc_combine(const efa_flash_partials* part, void* O, int o_dtype,
                               int row0, int rows, const efa_flash_params* p, void* stream);
 
+/* Size of the fixed device array that efa_flash_attn_tc_forward_noalloc keeps its split-KV partials in. */
+#define EFA_STATIC_SCRATCH_BYTES (8u << 20)
+
+/* Attention for rows q_start .. q_start+q_rows with split-KV, partials and merge in one call, and
+ * without any device allocation: not by the caller, not by this library. It has no counterpart in
+ * the reference, whose callers always allocate the partials workspace themselves
+ * (alloc_workspace). It is for callers that cannot get device memory when they call: a process
+ * whose memory pool already owns the whole GPU, where a plain cudaMalloc fails, or a loop that
+ * cannot afford the device-wide synchronisation an allocation implies.
+ * The partials live in a fixed array of EFA_STATIC_SCRATCH_BYTES inside the library (every GPU that
+ * loads the library holds that much until the process exits). The call is rejected, with a message
+ * that names the sizes, when p->split * q_rows * (H_local*d_h + 2*H_local) * 4 exceeds it.
+ * O: [q_rows][H_local*d_h] in o_dtype, written for every p->split >= 1. No tile counters.
+ * The first call on a device looks up the array's device address and configures the kernel; make
+ * that first call before any stream capture starts. All calls share the one array and it keeps
+ * the previous call's contents (nothing in it needs clearing: each call writes every element it
+ * later reads). Two calls that overlap on the GPU (different streams, or different host threads) race on it:
+ * order them on one stream or with events. Kernels launched here do not report to
+ * efa_kernel_status. */
+int efa_flash_attn_tc_forward_noalloc(const void* Q, const void* K, const void* V,
+                                      void* O, int o_dtype, int q_start, int q_rows,
+                                      const efa_flash_params* p, void* stream);
+
 /* flash_attn_tc_check_params (flash_attn_tc.cuh:59-60, flash_attn_tc.cu:401-409):
  * NULL when the launch is legal, else a static description. */
 const char* efa_flash_attn_tc_check_params(const efa_flash_params* p, int q_rows);
