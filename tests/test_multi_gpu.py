@@ -1,0 +1,80 @@
+"""Two ranks on two GPUs (torchrun, NCCL + gloo): every output-writing mode against the CPU checker's
+sum over ranks (attn_tests.cu:27-60, 124-139), with the reference recipe's rank-specific weights.
+Skipped on a machine with fewer than two GPUs."""
+import os
+import subprocess
+import sys
+import textwrap
+
+import pytest
+
+from conftest import ROOT
+
+pytestmark = pytest.mark.gpu
+
+WORKER = textwrap.dedent("""
+    import os, sys
+    sys.path.insert(0, {root!r})
+    import numpy as np, torch, torch.distributed as dist
+    import __graft_entry__ as entry
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group(backend="cpu:gloo,cuda:nccl", device_id=torch.device("cuda", local))
+    pkg = entry.load_package(); oracle = entry.load_oracle()
+    ctx = pkg.make_ctx(pkg.World.from_torch(None, local_device=local), ncomm=3)
+    cases = [(512, 256, 8, 128, 2, 1, 0), (1024, 512, 8, 256, 2, 1, 1), (1024, 1024, 8, 64, 3, 1, 0),
+             (2048, 512, 8, 128, 2, 4, 1), (512, 256, 4, 64, 2, 2, 0)]
+    reduces = {reduces!r}
+    ok = True
+    for S, d, H, tile, nbuf, split, causal in cases:
+        p = pkg.make_params(S, d, H, tile, nbuf, split, causal, world)
+        assert pkg.attn_check_params(p) is None
+        per_rank, mine = [], None
+        for r in range(world):
+            Q, K, V, W = oracle.ref_inputs(S, d, H, world, r, 42)
+            bits = tuple(oracle.round_f16(x) for x in (Q, K, V, W))
+            per_rank.append(tuple(oracle.widen_f16(b) for b in bits))
+            if r == rank:
+                mine = bits
+        ref = oracle.block_rows(per_rank, d, causal)
+        dev = [torch.from_numpy(b.view(np.float16)).cuda() for b in mine]
+        w = pkg.Weights(*(t.data_ptr() for t in dev))
+        for reduce in reduces:
+            p.reduce = reduce
+            for name in (("megatron", "sync", "overlap", "stream") if reduce == 0 else ("stream",)):
+                out = torch.full((S, d), float("nan"), dtype=torch.float16, device="cuda")
+                pkg.kernel_status_reset()
+                pkg.run_mode(ctx, pkg.parse_mode(name), w, out, p)
+                torch.cuda.synchronize()
+                ma, mr = oracle.compare(out.float().cpu().numpy(), ref)
+                good = bool(np.isfinite(ma)) and ma <= 2e-3 and ma <= 1e-2 * mr and pkg.kernel_status()[0] == 0
+                ok &= good
+                print(f"rank {{rank}} S={{S}} d={{d}} split={{split}} causal={{causal}} reduce={{reduce}} {{name}}: max_abs={{ma:.3e}} max_ref={{mr:.3e}} {{'PASS' if good else 'FAIL'}}", flush=True)
+    flag = torch.tensor([1 if ok else 0])
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    pkg.destroy_ctx(ctx)
+    dist.barrier()
+    dist.destroy_process_group()
+    sys.exit(0 if int(flag[0]) == 1 else 1)
+""")
+
+
+def run_workers(tmp_path, nproc, reduces):
+    import torch
+    if torch.cuda.device_count() < nproc:
+        pytest.skip(f"needs {nproc} GPUs")
+    script = tmp_path / "worker.py"
+    script.write_text(WORKER.format(root=ROOT, reduces=reduces))
+    port = 29600 + (os.getpid() % 1000)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+                        "--master-addr", "127.0.0.1", "--master-port", str(port), str(script)],
+                       capture_output=True, text=True, timeout=1500, env=env)
+    print(r.stdout[-6000:])
+    assert r.returncode == 0, r.stdout[-4000:] + r.stderr[-4000:]
+    assert "FAIL" not in r.stdout
+
+
+def test_two_ranks_nccl_reduction(tmp_path):
+    run_workers(tmp_path, 2, (0,))
