@@ -1,0 +1,35 @@
+// Kernel arguments shared by the attention kernels.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+namespace efa {
+
+struct FaArgs {
+    float*  O32;
+    __half* O16;
+    float*  O_part;
+    float*  m_part;
+    float*  l_part;
+    int     part_rows;
+    int     q_start, q_rows, S, H_local, nsplit, kv_len, causal;
+    float   scale_log2e;
+    int*    tile_counters;
+    int     tile_rows;
+    int*    status;
+};
+
+__device__ __forceinline__ float ex2(float x)
+{
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// Warp-specialised two-tile kernel (fa_fwd_ws_sm100.cu), d_h = 64 or 128.
+int fa_forward_ws(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FaArgs& a,
+                  int d_h, bool out_f16, cudaStream_t stream);
+
+}  // namespace efa

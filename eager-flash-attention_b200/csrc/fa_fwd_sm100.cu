@@ -12,11 +12,13 @@
 // memory and B = V from shared memory in MN-major form; O stays in tensor memory for the whole
 // key sweep and is rescaled there only when a row maximum moved.
 #include "fa_fwd_sm100.cuh"
+#include "fa_args.cuh"
 #include "host_util.h"
 #include "sm100_ptx.cuh"
 
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -41,27 +43,6 @@ struct FaCfg {
     static constexpr int TMEM_COLS  = 256;                       // S/P: 128 columns, O: D columns
     static constexpr int OCH        = D >= 32 ? 32 : 16;         // O columns per tcgen05.ld
 };
-
-struct FaArgs {
-    float*  O32;
-    __half* O16;
-    float*  O_part;
-    float*  m_part;
-    float*  l_part;
-    int     part_rows;
-    int     q_start, q_rows, S, H_local, nsplit, kv_len, causal;
-    float   scale_log2e;
-    int*    tile_counters;
-    int     tile_rows;
-    int*    status;
-};
-
-__device__ __forceinline__ float ex2(float x)
-{
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
 
 template <int D, bool OUT_F16>
 __global__ void __launch_bounds__(128)
@@ -491,8 +472,13 @@ int fa_forward(const void* Q, const void* K, const void* V, void* O, int o_dtype
     a.tile_counters = tile_counters; a.tile_rows = tile_rows;
     a.status = kernel_status_word();
 
-    dim3 grid(p.H_local * p.split, (q_rows + FA_BM - 1) / FA_BM);
     const bool f16 = (o_dtype == EFA_F16);
+    // d_h = 64 / 128 run on the warp-specialised two-tile kernel; EFA_ATTN_ONE_TILE=1 (a diagnostics
+    // switch, like the reference's --no_prio) keeps them on the one-tile kernel below for A/B timing.
+    static const bool one_tile_only = [] { const char* e = getenv("EFA_ATTN_ONE_TILE"); return e && e[0] == '1'; }();
+    if ((p.d_h == 64 || p.d_h == 128) && !one_tile_only)
+        return fa_forward_ws(tq, tk, tv, a, p.d_h, f16, stream);
+    dim3 grid(p.H_local * p.split, (q_rows + FA_BM - 1) / FA_BM);
     switch (p.d_h) {
         case 16:  return f16 ? launch_fa<16, true>(tq, tk, tv, a, grid, stream)  : launch_fa<16, false>(tq, tk, tv, a, grid, stream);
         case 32:  return f16 ? launch_fa<32, true>(tq, tk, tv, a, grid, stream)  : launch_fa<32, false>(tq, tk, tv, a, grid, stream);

@@ -1,0 +1,426 @@
+// Warp-specialised FlashAttention forward for sm_100a, d_h = 64 or 128: the fast path behind
+// flash_attn_tc_forward (flash_attn_tc.cu:73-312 of eager-flash-attention), same interface and
+// semantics as the one-tile kernel in fa_fwd_sm100.cu.
+//
+// One CTA = 256 query rows (two 128-row Q tiles) of one (head, split), 384 threads:
+//   warps 0-3   softmax of Q tile 0        (one thread per row; registers raised with setmaxnreg)
+//   warps 4-7   softmax of Q tile 1
+//   warp  8     TMA producer: Q tiles once, then K and V 128-key stages through a ring
+//   warp  9     tcgen05.mma issuer; owns the tensor-memory allocation
+//   warps 10-11 idle (they give their registers to the softmax warps)
+// Both Q tiles share each K/V stage, which halves the L2 -> shared-memory traffic per FLOP. The MMA
+// warp interleaves the tiles so that while one tile's softmax runs on the SIMT pipes the tensor
+// pipe executes the other tile's P*V and the next Q*K^T:
+//     ... PV0(j) QK0(j+1) | PV1(j) QK1(j+1) | PV0(j+1) QK0(j+2) | ...
+// Tensor memory (512 columns): S0/P0 [0,128) S1/P1 [128,256) O0 [256,256+D) O1 [384,384+D).
+// O is rescaled in tensor memory by the softmax warps themselves, and only when a row maximum grew
+// by more than 2^8 since the value last used as the exponent offset (P then stays below 256, well
+// inside fp16); the final division by the row sum makes the result independent of the offset.
+//
+// All waits are bounded; a warp leaves its loop as a whole when a wait fails, every other role then
+// runs into its own bounded wait or sees the CTA's abort word, and the CTA frees its tensor memory.
+#include "fa_fwd_sm100.cuh"
+#include "fa_args.cuh"
+#include "host_util.h"
+#include "sm100_ptx.cuh"
+
+#include <cmath>
+
+namespace efa {
+
+namespace {
+
+constexpr int WS_BM = 128;          // rows per Q tile
+constexpr int WS_BN = 128;          // keys per stage
+constexpr int WS_THREADS = 384;
+constexpr float kNegInfW = -INFINITY;
+constexpr float kRescaleThreshold = 8.0f;   // log2 units
+
+template <int D>
+struct WsCfg {
+    static constexpr int SWB        = 128;
+    static constexpr int BOXC       = 64;
+    static constexpr int NBOX       = D / 64;
+    static constexpr int BOX_BYTES  = 128 * SWB;                 // 16 KB
+    static constexpr int TILE_BYTES = 128 * D * 2;
+    static constexpr int NSTAGE     = D == 128 ? 2 : 4;
+    static constexpr int SMEM_BYTES = TILE_BYTES * (2 + 2 * NSTAGE) + 1024;
+    static constexpr int TMEM_COLS  = 512;
+};
+
+__device__ __forceinline__ void setmaxnreg_dec_56() { asm volatile("setmaxnreg.dec.sync.aligned.u32 56;"); }
+__device__ __forceinline__ void setmaxnreg_inc_224() { asm volatile("setmaxnreg.inc.sync.aligned.u32 224;"); }
+
+template <int D, bool OUT_F16>
+__global__ void __launch_bounds__(WS_THREADS, 1)
+fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ,
+                 const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV,
+                 const FaArgs a)
+{
+    using C = WsCfg<D>;
+    constexpr uint32_t SWZ = swizzle_code(128);
+    constexpr uint32_t IDESC_QK = idesc_f16_f32(WS_BM, WS_BN, 0, 0);
+    constexpr uint32_t IDESC_PV = idesc_f16_f32(WS_BM, D, 0, 1);
+    constexpr int NST = C::NSTAGE;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* sQ = smem;                                   // 2 tiles
+    uint8_t* sK = sQ + 2 * C::TILE_BYTES;                 // NST stages
+    uint8_t* sV = sK + NST * C::TILE_BYTES;               // NST stages
+
+    __shared__ __align__(8) uint64_t q_full[2];
+    __shared__ __align__(8) uint64_t k_full[NST], k_empty[NST], v_full[NST], v_empty[NST];
+    __shared__ __align__(8) uint64_t s_full[2], p_full[2], o_done[2];
+    __shared__ uint32_t tmem_base_smem;
+    __shared__ int abort_word;
+    __shared__ int half_done[2][2];                       // [tile][64-row half]: warps that finished their stores
+
+    const int tid  = threadIdx.x;
+    const int warp = tid >> 5;
+    const int lane = tid & 31;
+
+    const int head  = blockIdx.x % a.H_local;
+    const int split = blockIdx.x / a.H_local;
+    const int block_row0 = blockIdx.y * (2 * WS_BM);
+    const int rows_valid = min(2 * WS_BM, a.q_rows - block_row0);      // 64, 128, 192 or 256
+    const int kv_lo = split * a.kv_len;
+    const int kv_hi = kv_lo + a.kv_len;
+
+    // Per Q tile: first absolute row, valid rows, number of key stages.
+    int q_abs0[2], rows_q[2], nblk[2];
+    #pragma unroll
+    for (int q = 0; q < 2; q++) {
+        q_abs0[q] = a.q_start + block_row0 + q * WS_BM;
+        rows_q[q] = max(0, min(WS_BM, rows_valid - q * WS_BM));
+        const int kv_end = a.causal ? min(kv_hi, q_abs0[q] + rows_q[q]) : kv_hi;
+        nblk[q] = (rows_q[q] > 0 && kv_end > kv_lo) ? (kv_end - kv_lo + WS_BN - 1) / WS_BN : 0;
+    }
+    const int nblk_max = max(nblk[0], nblk[1]);
+
+    if (tid == 0) {
+        abort_word = 0;
+        half_done[0][0] = half_done[0][1] = half_done[1][0] = half_done[1][1] = 0;
+        for (int q = 0; q < 2; q++) {
+            mbar_init(&q_full[q], 1);
+            mbar_init(&s_full[q], 1);
+            mbar_init(&p_full[q], WS_BM);
+            mbar_init(&o_done[q], 1);
+        }
+        for (int s = 0; s < NST; s++) {
+            mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
+            mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
+        }
+        mbar_fence_init();
+        tma_prefetch_desc(&tmQ);
+        tma_prefetch_desc(&tmK);
+        tma_prefetch_desc(&tmV);
+    }
+    if (warp == 9) tmem_alloc(&tmem_base_smem, C::TMEM_COLS);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_base_smem;
+
+    if (warp >= 8) {
+        // =====================================================================================
+        // Producer / MMA warpgroup
+        // =====================================================================================
+        setmaxnreg_dec_56();
+        if (warp == 8 && lane == 0) {
+            // ---- TMA producer
+            auto load_tile = [&](uint8_t* dst, const CUtensorMap* tm, uint64_t* bar, int row) {
+                mbar_expect_tx(bar, C::TILE_BYTES);
+                #pragma unroll
+                for (int b = 0; b < C::NBOX; b++)
+                    tma_load_3d(dst + b * C::BOX_BYTES, tm, bar, b * C::BOXC, row, head);
+            };
+            for (int q = 0; q < 2; q++)
+                if (nblk[q] > 0) load_tile(sQ + q * C::TILE_BYTES, &tmQ, &q_full[q], q_abs0[q]);
+            for (int j = 0; j < nblk_max; j++) {
+                const int s = j % NST, u = j / NST;
+                if (u > 0 && !mbar_wait(&k_empty[s], (uint32_t)((u - 1) & 1), &abort_word, 21)) break;
+                load_tile(sK + s * C::TILE_BYTES, &tmK, &k_full[s], kv_lo + j * WS_BN);
+                if (u > 0 && !mbar_wait(&v_empty[s], (uint32_t)((u - 1) & 1), &abort_word, 22)) break;
+                load_tile(sV + s * C::TILE_BYTES, &tmV, &v_full[s], kv_lo + j * WS_BN);
+            }
+        } else if (warp == 9 && lane == 0) {
+            // ---- MMA issuer
+            auto issue_qk = [&](int q, int stage) {
+                const uint32_t qa = smem_u32(sQ + q * C::TILE_BYTES);
+                const uint32_t ka = smem_u32(sK + stage * C::TILE_BYTES);
+                #pragma unroll
+                for (int ks = 0; ks < D / 16; ks++) {
+                    const uint32_t off = (uint32_t)((ks * 16) / C::BOXC) * C::BOX_BYTES + (uint32_t)((ks * 16) % C::BOXC) * 2u;
+                    tc_mma_ss(tmem_base + q * 128, smem_desc(qa + off, 16, 1024, SWZ), smem_desc(ka + off, 16, 1024, SWZ),
+                              IDESC_QK, ks > 0 ? 1u : 0u);
+                }
+            };
+            auto issue_pv = [&](int q, int stage, bool first) {
+                const uint32_t va = smem_u32(sV + stage * C::TILE_BYTES);
+                #pragma unroll
+                for (int ks = 0; ks < WS_BN / 16; ks++)
+                    tc_mma_ts(tmem_base + 256 + q * 128, tmem_base + q * 128 + ks * 8,
+                              smem_desc(va + ks * 16 * 128, C::BOX_BYTES, 1024, SWZ), IDESC_PV, (!first || ks > 0) ? 1u : 0u);
+            };
+            bool ok = true;
+            if (nblk_max > 0) {
+                ok = mbar_wait(&k_full[0], 0, &abort_word, 23);
+                for (int q = 0; q < 2 && ok; q++) {
+                    if (nblk[q] > 0) {
+                        ok = mbar_wait(&q_full[q], 0, &abort_word, 24);
+                        if (!ok) break;
+                        tc_fence_after_sync();
+                        issue_qk(q, 0);
+                        tc_commit(&s_full[q]);
+                    }
+                }
+                if (ok) tc_commit(&k_empty[0]);
+            }
+            for (int j = 0; j < nblk_max && ok; j++) {
+                const int s = j % NST;
+                ok = mbar_wait(&v_full[s], (uint32_t)((j / NST) & 1), &abort_word, 25);
+                if (!ok) break;
+                bool k_next_ready = false;
+                for (int q = 0; q < 2 && ok; q++) {
+                    if (j >= nblk[q]) continue;
+                    ok = mbar_wait(&p_full[q], (uint32_t)(j & 1), &abort_word, 26);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    issue_pv(q, s, j == 0);
+                    if (j + 1 < nblk[q]) {
+                        const int ns = (j + 1) % NST;
+                        if (!k_next_ready) {
+                            ok = mbar_wait(&k_full[ns], (uint32_t)(((j + 1) / NST) & 1), &abort_word, 27);
+                            if (!ok) break;
+                            tc_fence_after_sync();
+                            k_next_ready = true;
+                        }
+                        issue_qk(q, ns);
+                        tc_commit(&s_full[q]);
+                    } else {
+                        tc_commit(&o_done[q]);
+                    }
+                }
+                if (!ok) break;
+                tc_commit(&v_empty[s]);
+                if (j + 1 < nblk_max) tc_commit(&k_empty[(j + 1) % NST]);
+            }
+        }
+    } else {
+        // =====================================================================================
+        // Softmax warpgroups: tile q = warp / 4, row = thread index within the warpgroup
+        // =====================================================================================
+        setmaxnreg_inc_224();
+        const int q = warp >> 2;
+        const int row = tid - q * WS_BM;
+        const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+        const uint32_t tmem_S = tmem_base + q * 128 + lane_base;
+        const uint32_t tmem_O = tmem_base + 256 + q * 128 + lane_base;
+        const int my_rows = rows_q[q];
+        const int my_nblk = nblk[q];
+        const int my_abs0 = q_abs0[q];
+
+        float m_ref = kNegInfW;     // exponent offset in use (a past row maximum), scaled by scale*log2(e)
+        float m_true = kNegInfW;    // true running row maximum, same scaling
+        float l_run = 0.f;          // running denominator relative to m_ref
+        bool ok = true;
+
+        for (int j = 0; j < my_nblk; j++) {
+            const int kb = kv_lo + j * WS_BN;
+            ok = __all_sync(0xffffffffu, mbar_wait(&s_full[q], (uint32_t)(j & 1), &abort_word, 31));
+            if (!ok) break;
+            tc_fence_after_sync();
+
+            uint32_t su[4][32];
+            #pragma unroll
+            for (int c = 0; c < 4; c++) tmem_ld32(tmem_S + c * 32, su[c]);
+            tmem_wait_ld();
+
+            const bool need_mask = (kb + WS_BN > kv_hi) || (a.causal && kb + WS_BN - 1 > my_abs0);
+            if (need_mask) {
+                int lim = kv_hi - 1 - kb;
+                if (a.causal) lim = min(lim, my_abs0 + row - kb);
+                #pragma unroll
+                for (int c = 0; c < 4; c++)
+                    #pragma unroll
+                    for (int i = 0; i < 32; i++)
+                        if (c * 32 + i > lim) su[c][i] = 0xff800000u;
+            }
+
+            float mx0 = kNegInfW, mx1 = kNegInfW, mx2 = kNegInfW, mx3 = kNegInfW;
+            #pragma unroll
+            for (int i = 0; i < 32; i++) {
+                mx0 = fmaxf(mx0, __uint_as_float(su[0][i]));
+                mx1 = fmaxf(mx1, __uint_as_float(su[1][i]));
+                mx2 = fmaxf(mx2, __uint_as_float(su[2][i]));
+                mx3 = fmaxf(mx3, __uint_as_float(su[3][i]));
+            }
+            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+            m_true = fmaxf(m_true, mx * a.scale_log2e);
+
+            // Move the exponent offset only when the maximum grew by more than the threshold.
+            float alpha = 1.f;
+            if (m_true - m_ref > kRescaleThreshold || m_ref == kNegInfW) {     // (-inf) - (-inf) is NaN: second test
+                const float m_new = m_true;
+                const float m_use = (m_new == kNegInfW) ? 0.f : m_new;
+                alpha = (m_ref == kNegInfW) ? 0.f : ex2(m_ref - m_use);
+                m_ref = m_new;
+            }
+            const float m_off = (m_ref == kNegInfW) ? 0.f : m_ref;
+
+            float ps0 = 0.f, ps1 = 0.f;
+            #pragma unroll
+            for (int c = 0; c < 4; c++) {
+                uint32_t pk[16];
+                #pragma unroll
+                for (int i = 0; i < 16; i++) {
+                    const float p0 = ex2(fmaf(__uint_as_float(su[c][2 * i]),     a.scale_log2e, -m_off));
+                    const float p1 = ex2(fmaf(__uint_as_float(su[c][2 * i + 1]), a.scale_log2e, -m_off));
+                    ps0 += p0;
+                    ps1 += p1;
+                    pk[i] = pack_f16x2(p0, p1);
+                }
+                tmem_st16(tmem_S + c * 16, pk);
+            }
+            l_run = l_run * alpha + (ps0 + ps1);
+
+            // S(j) complete implies PV(j-1) of this tile complete (the tensor pipe runs in order), and
+            // PV(j) is not issued before this thread arrives below: O may be rescaled here.
+            if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+                #pragma unroll
+                for (int c = 0; c < D / 32; c++) {
+                    uint32_t o[32];
+                    tmem_ld32(tmem_O + c * 32, o);
+                    tmem_wait_ld();
+                    #pragma unroll
+                    for (int i = 0; i < 32; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                    tmem_st32(tmem_O + c * 32, o);
+                }
+            }
+            tmem_wait_st();
+            tc_fence_before_sync();
+            mbar_arrive(&p_full[q]);
+        }
+
+        if (ok && my_nblk > 0) {
+            ok = __all_sync(0xffffffffu, mbar_wait(&o_done[q], 0, &abort_word, 32));
+            tc_fence_after_sync();
+        }
+
+        // ---- epilogue: this thread's row (warps take this branch as a whole: my_rows is 0, 64 or 128)
+        if (ok && (warp & 3) * 32 < my_rows) {
+            const size_t ld_o = (size_t)a.H_local * D;
+            const size_t orow = (size_t)block_row0 + q * WS_BM + row;
+            float mult;
+            float*  dst32 = nullptr;
+            __half* dst16 = nullptr;
+            if (a.nsplit == 1) {
+                mult = 1.f / l_run;
+                if constexpr (OUT_F16) dst16 = a.O16 + orow * ld_o + (size_t)head * D;
+                else                   dst32 = a.O32 + orow * ld_o + (size_t)head * D;
+            } else {
+                // partials are stored relative to the true row maximum
+                mult = (m_true == kNegInfW) ? 0.f : ex2(m_ref - m_true);
+                dst32 = a.O_part + ((size_t)split * a.part_rows + orow) * ld_o + (size_t)head * D;
+                const size_t s0 = ((size_t)split * a.part_rows + orow) * a.H_local + head;
+                a.m_part[s0] = m_true;
+                a.l_part[s0] = l_run * mult;
+            }
+            #pragma unroll
+            for (int c = 0; c < D / 16; c++) {
+                uint32_t o[16];
+                if (my_nblk > 0) {
+                    tmem_ld16(tmem_O + c * 16, o);
+                    tmem_wait_ld();
+                } else {
+                    #pragma unroll
+                    for (int i = 0; i < 16; i++) o[i] = 0u;
+                }
+                if (dst16) {
+                    uint4 v0, v1;
+                    v0.x = pack_f16x2(__uint_as_float(o[0]) * mult,  __uint_as_float(o[1]) * mult);
+                    v0.y = pack_f16x2(__uint_as_float(o[2]) * mult,  __uint_as_float(o[3]) * mult);
+                    v0.z = pack_f16x2(__uint_as_float(o[4]) * mult,  __uint_as_float(o[5]) * mult);
+                    v0.w = pack_f16x2(__uint_as_float(o[6]) * mult,  __uint_as_float(o[7]) * mult);
+                    v1.x = pack_f16x2(__uint_as_float(o[8]) * mult,  __uint_as_float(o[9]) * mult);
+                    v1.y = pack_f16x2(__uint_as_float(o[10]) * mult, __uint_as_float(o[11]) * mult);
+                    v1.z = pack_f16x2(__uint_as_float(o[12]) * mult, __uint_as_float(o[13]) * mult);
+                    v1.w = pack_f16x2(__uint_as_float(o[14]) * mult, __uint_as_float(o[15]) * mult);
+                    uint4* d = reinterpret_cast<uint4*>(dst16 + c * 16);
+                    d[0] = v0;
+                    d[1] = v1;
+                } else {
+                    float4* d = reinterpret_cast<float4*>(dst32 + c * 16);
+                    #pragma unroll
+                    for (int qd = 0; qd < 4; qd++)
+                        d[qd] = make_float4(__uint_as_float(o[4 * qd]) * mult, __uint_as_float(o[4 * qd + 1]) * mult,
+                                            __uint_as_float(o[4 * qd + 2]) * mult, __uint_as_float(o[4 * qd + 3]) * mult);
+                }
+            }
+
+            // ---- completion signal: one count per finished 64-row block, after its rows are visible.
+            // A 64-row block is two warps; the second of them to get here publishes the count.
+            if (a.tile_counters != nullptr) {
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) {
+                    const int half = (warp & 3) >> 1;
+                    if (atomicAdd(&half_done[q][half], 1) == 1) {
+                        __threadfence();
+                        atomicAdd(a.tile_counters + (block_row0 + q * WS_BM + half * 64) / a.tile_rows, 1);
+                    }
+                }
+            }
+        }
+    }
+
+    // ---- teardown (every thread of the CTA gets here, whatever happened above)
+    __syncwarp();
+    tc_fence_before_sync();
+    __syncthreads();
+    if (abort_word != 0) {
+        for (int i = 0; i < 64; i++) __nanosleep(100000);
+        if (tid == 0 && a.status != nullptr) {
+            if (atomicCAS(a.status, 0, (int)KS_WAIT_TIMEOUT) == 0) {
+                a.status[1] = (int)(blockIdx.y * gridDim.x + blockIdx.x);
+                a.status[2] = abort_word;
+            }
+        }
+        __syncthreads();
+    }
+    if (warp == 9) tmem_dealloc(tmem_base, C::TMEM_COLS);
+}
+
+template <int D, bool OUT_F16>
+int launch_ws(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FaArgs& args,
+              dim3 grid, cudaStream_t stream)
+{
+    using C = WsCfg<D>;
+    static bool configured[64] = {};
+    int dev = 0;
+    EFA_CUDA(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        EFA_CUDA(cudaFuncSetAttribute(fa_fwd_ws_kernel<D, OUT_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+        configured[dev] = true;
+    }
+    fa_fwd_ws_kernel<D, OUT_F16><<<grid, WS_THREADS, C::SMEM_BYTES, stream>>>(tq, tk, tv, args);
+    EFA_CUDA(cudaGetLastError());
+    return 0;
+}
+
+}  // namespace
+
+// Launch of the warp-specialised kernel; the caller has validated the arguments and built the maps.
+int fa_forward_ws(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FaArgs& a,
+                  int d_h, bool out_f16, cudaStream_t stream)
+{
+    dim3 grid(a.H_local * a.nsplit, (a.q_rows + 2 * WS_BM - 1) / (2 * WS_BM));
+    if (d_h == 64)  return out_f16 ? launch_ws<64, true>(tq, tk, tv, a, grid, stream)  : launch_ws<64, false>(tq, tk, tv, a, grid, stream);
+    if (d_h == 128) return out_f16 ? launch_ws<128, true>(tq, tk, tv, a, grid, stream) : launch_ws<128, false>(tq, tk, tv, a, grid, stream);
+    set_error("fa_forward_ws: d_h=%d is not handled by the warp-specialised kernel", d_h);
+    return 2;
+}
+
+}  // namespace efa
