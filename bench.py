@@ -165,7 +165,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--mode", default="stream", choices=["stream", "megatron"])
-    ap.add_argument("--reduce", default="nccl", choices=["nccl", "p2p"])
+    ap.add_argument("--reduce", default="auto", choices=["auto", "nccl", "p2p"],
+                    help="stream mode: per-group NCCL AllReduce, or the persistent projection+reduction kernel over "
+                         "peer memory; auto = whichever measured faster for this rank count")
+    ap.add_argument("--group-tiles", type=int, default=0, help="tiles per projection + AllReduce launch (0 = auto, 1 = per tile)")
     ap.add_argument("--cpu-rows", type=int, default=48, help="query rows of the CPU baseline sample (0 = skip)")
     ap.add_argument("--S", type=int, default=WORKLOAD["S"], help="override the sequence length (profiling captures only)")
     args = ap.parse_args()
@@ -204,7 +207,12 @@ def main():
     why = pkg.attn_check_params(p)
     if why:
         raise SystemExit(f"invalid workload for {world_size} ranks: {why}")
+    if args.reduce == "auto":
+        # Measured on 8xB200 for this workload: the fused kernel wins with one or two ranks, grouped NCCL
+        # AllReduces with four and eight (profiles/ has the table).
+        args.reduce = "p2p" if world_size <= 2 else "nccl"
     p.reduce = pkg.REDUCE_P2P if args.reduce == "p2p" else pkg.REDUCE_NCCL
+    p.group_tiles = args.group_tiles
     mode = pkg.parse_mode(args.mode)
 
     # Synthetic inputs in pinned host memory (N(0,1) Q/K/V, W_O ~ N(0, 1/d)), then resident copies.
@@ -295,7 +303,7 @@ def main():
     line = None
     if rank == 0:
         cpu = None
-        if args.cpu_rows > 0:
+        if args.cpu_rows > 0 and world_size == 1:      # the CPU baseline is reported at N=1 only
             oracle = entry.load_oracle()
             cpu = cpu_baseline(pkg, oracle, p, [h.numpy().view(np.uint16) for h in host], args.cpu_rows)
         line = dict(
@@ -303,7 +311,8 @@ def main():
             ms_per_step=ms, higher_is_better=False, scaling="strong", vs_baseline=None, dtype="f16 (f32 accumulate)",
             data="synthetic",
             config=dict(workload=f"S={p.S} H={p.H} d_h={p.d_h} causal tile={p.tile} ncomm={W['ncomm']} TP={world_size}",
-                        mode=args.mode, reduce=args.reduce, l2="256 MB buffer written between steps",
+                        mode=args.mode, reduce=args.reduce, group_tiles=args.group_tiles or "auto (S/8 rows per launch)",
+                        l2="256 MB buffer written between steps",
                         inputs="Q,K,V ~ N(0,1) fp16 [H_local][S][d_h]; W_O ~ N(0,1/d) fp16; seed 42"),
             tokens_per_s=p.S / (ms * 1e-3),
             modes_ms=modes, exposed_comm_frac=exposed,

@@ -50,7 +50,7 @@ class Params(C.Structure):
                 ("H_local", C.c_int), ("d_h", C.c_int), ("d_local", C.c_int),
                 ("tile", C.c_int), ("num_tiles", C.c_int),
                 ("nbuf", C.c_int), ("split", C.c_int), ("causal", C.c_int),
-                ("skip_proj", C.c_int), ("skip_comm", C.c_int), ("reduce", C.c_int),
+                ("skip_proj", C.c_int), ("skip_comm", C.c_int), ("reduce", C.c_int), ("group_tiles", C.c_int),
                 ("flash_tc", FlashParams)]
 
 

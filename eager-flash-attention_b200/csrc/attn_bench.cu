@@ -79,7 +79,7 @@ static void usage(const char* prog)
         "          [--nbuf 2] [--split 1] [--ncomm 1] [--warmup 3] [--trials 10]\n"
         "          [--modes attn,attn_tiled,megatron,sync,overlap,stream,comm] [--no-header]\n"
         "          [--causal] [--proj fp16] [--no_prio] [--no_proj] [--no_comm]\n"
-        "          [--reduce nccl|p2p] [--data normal|ref] [--seed 42]\n", prog);
+        "          [--reduce nccl|p2p] [--group_tiles 0] [--data normal|ref] [--seed 42]\n", prog);
 }
 
 int main(int argc, char** argv)
@@ -141,6 +141,7 @@ int main(int argc, char** argv)
     EFA_OK(efa_make_params(&p, S, d, H, tile, nbuf, split, causal, world));
     p.skip_proj = has_flag(argc, argv, "--no_proj");
     p.skip_comm = has_flag(argc, argv, "--no_comm");
+    p.group_tiles = arg_int(argc, argv, "--group_tiles", 0);
     if (std::strcmp(reduce, "p2p") == 0) p.reduce = EFA_REDUCE_P2P;
     else if (std::strcmp(reduce, "nccl") != 0) fail("--reduce must be nccl or p2p");
     if (const char* why = efa_attn_check_params(&p)) {

@@ -61,7 +61,8 @@ const DriverApi* driver_api()
     if (resolve("cuTensorMapEncodeTiled", (void**)&api.cuTensorMapEncodeTiled) ||
         resolve("cuStreamWaitValue32", (void**)&api.cuStreamWaitValue32) ||
         resolve("cuStreamWriteValue32", (void**)&api.cuStreamWriteValue32) ||
-        resolve("cuGetErrorString", (void**)&api.cuGetErrorString)) {
+        resolve("cuGetErrorString", (void**)&api.cuGetErrorString) ||
+        resolve("cuMemGetAddressRange", (void**)&api.cuMemGetAddressRange)) {
         state = -1;
         return nullptr;
     }

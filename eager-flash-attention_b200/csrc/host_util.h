@@ -29,6 +29,7 @@ struct DriverApi {
     CUresult (*cuStreamWaitValue32)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
     CUresult (*cuStreamWriteValue32)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
     CUresult (*cuGetErrorString)(CUresult, const char**);
+    CUresult (*cuMemGetAddressRange)(CUdeviceptr*, size_t*, CUdeviceptr);
 };
 // nullptr (with the error recorded) when the driver is not available.
 const DriverApi* driver_api();

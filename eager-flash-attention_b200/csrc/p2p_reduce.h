@@ -6,10 +6,16 @@
 
 namespace efa {
 
+// 1 when the fused path can run this problem; otherwise 0 and *why says what is in the way.
+int p2p_supported(const efa_params& p, const char** why);
+// Tile counters the attention kernel must signal into for the fused path (never reset: targets grow per run).
+int* p2p_counters(efa_ctx* c);
+
 // Exchange IPC handles of the staging buffers for this shape (collective; cached in the context).
 int p2p_prepare(efa_ctx* c, const efa_params& p, void* output);
-// Enqueue projection + reduction of tile t on the projection stream.
-int p2p_tile(efa_ctx* c, const efa_params& p, const efa_weights& w, const void* O_tile, int t, int* launches);
+// Launch the persistent projection + reduction kernel of this run on the projection stream
+// (first call of a run launches; later calls in the same run do nothing). O_all: fp16 [S][d_local].
+int p2p_tile(efa_ctx* c, const efa_params& p, const efa_weights& w, const void* O_all, int t, int* launches);
 // Enqueue the final hand-shake that makes every rank's output complete.
 int p2p_finish(efa_ctx* c, const efa_params& p);
 void p2p_destroy(efa_ctx* c);

@@ -207,6 +207,7 @@ extern "C" int efa_make_params(efa_params* out, int S, int d, int H, int tile, i
     p.nbuf = nbuf; p.split = split; p.causal = causal;
     p.skip_proj = 0; p.skip_comm = 0;
     p.reduce = EFA_REDUCE_NCCL;
+    p.group_tiles = 0;
     const float scale = p.d_h > 0 ? 1.0f / sqrtf((float)p.d_h) : 0.f;
     p.flash_tc = efa_flash_params{S, p.d_h, p.H_local, split, causal, scale};
     *out = p;

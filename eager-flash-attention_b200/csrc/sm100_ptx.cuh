@@ -83,7 +83,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity)
 
 // Bounded wait. `abort_word` lives in shared memory and is set by whichever thread of the CTA
 // first gives up; every other waiter sees it and gives up too.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_word, int site)
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_word, int site,
+                                          unsigned long long limit_ns = kWaitLimitNs)
 {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = globaltimer_ns();
@@ -92,7 +93,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
         if (mbar_try_wait(bar, parity)) return true;
         if ((++spins & 63) == 0) {
             if (*abort_word != 0) return false;
-            if (globaltimer_ns() - t0 > kWaitLimitNs) {
+            if (globaltimer_ns() - t0 > limit_ns) {
                 *abort_word = site;
                 return false;
             }

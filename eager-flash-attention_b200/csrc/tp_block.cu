@@ -278,7 +278,24 @@ int run_stream(Run& r, __half* output, efa_run_stats* st)
     const int target = efa_blocks_per_tile(&p);
     cudaEvent_t reset_done = c->events[p.num_tiles];
     const bool fused = (p.reduce == EFA_REDUCE_P2P) && !p.skip_comm && !p.skip_proj;
-    if (fused && p2p_prepare(c, p, output)) return 1;
+    if (fused) {
+        // One persistent kernel does projection and reduction of every tile beside the attention kernel:
+        // it polls the tile counters itself, so nothing is enqueued per tile. The attention kernel is
+        // launched first: the first launch of a kernel may have to load its code, which can wait for
+        // running kernels to drain, and a kernel that spins on the attention kernel's counters must
+        // never be what that load waits for. The persistent CTAs (high-priority stream) take SMs as
+        // the first attention CTAs retire.
+        if (p2p_prepare(c, p, output)) return 1;
+        if (world_barrier(c->world)) return 1;
+        const double t0f = now_ms();
+        EFA_CUDA(cudaEventRecord(c->ev_t0, c->compute_stream));
+        if (r.attention_raw(O_all, p.S, 0, p.S, c->compute_stream, p2p_counters(c), p.tile)) return 1;
+        EFA_CUDA(cudaEventRecord(c->ev_t1, c->compute_stream));
+        if (p2p_tile(c, p, r.w, O_all, 0, &r.launches)) return 1;
+        if (sync_stream(c, c->compute_stream, nullptr, 0)) return 1;
+        if (sync_stream(c, c->proj_stream, nullptr, 0)) return 1;
+        return finish_timing(c, t0f, st, true, false, r.launches);
+    }
 
     if (world_barrier(c->world)) return 1;
     const double t0 = now_ms();
@@ -290,23 +307,30 @@ int run_stream(Run& r, __half* output, efa_run_stats* st)
     EFA_CUDA(cudaEventRecord(c->ev_t1, c->compute_stream));
 
     EFA_CUDA(cudaStreamWaitEvent(c->proj_stream, reset_done, 0));   // never observe a stale counter
-    for (int t = 0; t < p.num_tiles; t++) {
-        EFA_CU(api->cuStreamWaitValue32((CUstream)c->proj_stream, (CUdeviceptr)(counters + t),
-                                        (cuuint32_t)target, CU_STREAM_WAIT_VALUE_GEQ));
-        __half* O_t = O_all + (size_t)t * p.tile * p.d_local;
-        __half* S_t = send_buf + (size_t)t * p.tile * p.d;
-        if (r.combine(O_t, p.S, t * p.tile, p.tile, c->proj_stream)) return 1;
-        if (fused) {
-            if (p2p_tile(c, p, r.w, O_t, t, &r.launches)) return 1;
-            continue;
-        }
-        if (r.project(O_t, S_t, p.tile)) return 1;
-        EFA_CUDA(cudaEventRecord(c->events[t], c->proj_stream));
-        const int slot = t % c->ncomm;
-        EFA_CUDA(cudaStreamWaitEvent(c->comm_streams[slot], c->events[t], 0));
-        if (r.allreduce(slot, S_t, output + (size_t)t * p.tile * p.d, (size_t)p.tile * p.d)) return 1;
+    // Tiles are signalled one by one; the projection and the AllReduce are launched once per group of
+    // consecutive tiles, after a front-end wait on every counter of the group. group_tiles = 1 is the
+    // reference's schedule. Small tiles make one launch and one collective per tile cost more than the
+    // attention of the tile (a 128-row tile of the benchmark shape is a few microseconds of attention on
+    // eight GPUs), so the default groups about S/8 rows.
+    int gt = p.group_tiles;
+    if (gt <= 0) { gt = (p.S / 8) / p.tile; if (gt < 1) gt = 1; }
+    if (gt > p.num_tiles) gt = p.num_tiles;
+    int gidx = 0;
+    for (int t0g = 0; t0g < p.num_tiles; t0g += gt, gidx++) {
+        const int nt = (t0g + gt <= p.num_tiles) ? gt : p.num_tiles - t0g;
+        for (int t = t0g; t < t0g + nt; t++)
+            EFA_CU(api->cuStreamWaitValue32((CUstream)c->proj_stream, (CUdeviceptr)(counters + t),
+                                            (cuuint32_t)target, CU_STREAM_WAIT_VALUE_GEQ));
+        const int rows = nt * p.tile;
+        __half* O_t = O_all + (size_t)t0g * p.tile * p.d_local;
+        __half* S_t = send_buf + (size_t)t0g * p.tile * p.d;
+        if (r.combine(O_t, p.S, t0g * p.tile, rows, c->proj_stream)) return 1;
+        if (r.project(O_t, S_t, rows)) return 1;
+        EFA_CUDA(cudaEventRecord(c->events[gidx], c->proj_stream));
+        const int slot = gidx % c->ncomm;
+        EFA_CUDA(cudaStreamWaitEvent(c->comm_streams[slot], c->events[gidx], 0));
+        if (r.allreduce(slot, S_t, output + (size_t)t0g * p.tile * p.d, (size_t)rows * p.d)) return 1;
     }
-    if (fused && p2p_finish(c, p)) return 1;
     if (sync_stream(c, c->compute_stream, counters, p.num_tiles)) return 1;
     if (sync_stream(c, c->proj_stream, counters, p.num_tiles)) return 1;
     if (sync_comm_streams(c)) return 1;

@@ -137,6 +137,9 @@ typedef struct efa_params {
     int nbuf, split, causal;
     int skip_proj, skip_comm;
     int reduce;                 /* EFA_REDUCE_* */
+    int group_tiles;            /* stream mode, NCCL reduction: consecutive tiles handled by one projection +
+                                   AllReduce launch (each tile's counter is still waited on). 1 = the reference's
+                                   per-tile schedule; 0 = automatic (about S/8 rows per launch). */
     efa_flash_params flash_tc;
 } efa_params;
 

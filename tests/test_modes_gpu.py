@@ -105,3 +105,31 @@ def test_host_buffer_entry_point(pkg, oracle, torch_cuda, ctx):
     st = pkg.run_mode_host(ctx, pkg.MODE_STREAM, *pinned, out, p)
     assert st.wall_ms > 0
     assert_close(oracle, out.float().numpy(), ref)
+
+
+@pytest.mark.parametrize("case", [(512, 256, 8, 128, 0), (1024, 512, 8, 256, 1), (1024, 1024, 8, 64, 0), (2048, 1024, 8, 512, 1),
+                                  (448, 512, 4, 64, 1), (4096, 1024, 16, 128, 1)],
+                         ids=lambda c: "S%d_d%d_H%d_t%d_c%d" % c)
+def test_stream_mode_with_the_fused_projection_kernel_single_rank(pkg, oracle, torch_cuda, ctx, case):
+    """--reduce p2p on one rank: the persistent kernel polls the tile counters, projects each 128-row
+    block as it completes and writes the output directly (nothing to reduce). Run twice: tile counters
+    and flags are never reset between runs, the wait targets grow instead."""
+    torch = torch_cuda
+    S, d, H, tile, causal = case
+    p = pkg.make_params(S, d, H, tile, 2, 1, causal)
+    p.reduce = pkg.REDUCE_P2P
+    bits, vals = ref_inputs_f16(oracle, S, d, H, 1, 0, 42) if S <= 2048 else normal_inputs_f16(pkg, oracle, p, 0, 42)
+    rows = None if S <= 2048 else np.arange(0, S, 13, dtype=np.int32)
+    ref = oracle.block_rows([vals], d, causal, rows)
+    dev = to_dev(torch, bits)
+    w = pkg.Weights(*(t.data_ptr() for t in dev))
+    out = torch.full((S, d), float("nan"), dtype=torch.float16, device="cuda")
+    for rep in range(3):
+        out.fill_(float("nan"))
+        pkg.kernel_status_reset()
+        st = pkg.run_mode(ctx, pkg.MODE_STREAM, w, out, p)
+        torch.cuda.synchronize()
+        assert pkg.kernel_status()[0] == 0, pkg.kernel_status()
+        assert st.kernel_launches == 2
+        got = out.float().cpu().numpy()
+        assert_close(oracle, got if rows is None else got[rows], ref, f"rep {rep}")

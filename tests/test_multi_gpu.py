@@ -24,10 +24,15 @@ WORKER = textwrap.dedent("""
     pkg = entry.load_package(); oracle = entry.load_oracle()
     ctx = pkg.make_ctx(pkg.World.from_torch(None, local_device=local), ncomm=3)
     cases = [(512, 256, 8, 128, 2, 1, 0), (1024, 512, 8, 256, 2, 1, 1), (1024, 1024, 8, 64, 3, 1, 0),
-             (2048, 512, 8, 128, 2, 4, 1), (512, 256, 4, 64, 2, 2, 0)]
+             (2048, 512, 8, 128, 2, 4, 1), (512, 256, 4, 64, 2, 2, 0), (448, 512, 8, 64, 2, 1, 1)]
     reduces = {reduces!r}
     ok = True
+    outs = {{}}
+    if world > 2:
+        cases = [(1024, 1024, 8, 128, 2, 1, 1), (2048, 2048, 16, 256, 2, 1, 0), (1024, 512, 8, 256, 2, 1, 0), (960, 1024, 8, 64, 3, 1, 1)]
     for S, d, H, tile, nbuf, split, causal in cases:
+        if H % world != 0:
+            continue
         p = pkg.make_params(S, d, H, tile, nbuf, split, causal, world)
         assert pkg.attn_check_params(p) is None
         per_rank, mine = [], None
@@ -41,14 +46,26 @@ WORKER = textwrap.dedent("""
         dev = [torch.from_numpy(b.view(np.float16)).cuda() for b in mine]
         w = pkg.Weights(*(t.data_ptr() for t in dev))
         for reduce in reduces:
+            if reduce == 1 and (split != 1 or d % (128 * world) != 0):
+                continue
             p.reduce = reduce
             for name in (("megatron", "sync", "overlap", "stream") if reduce == 0 else ("stream",)):
-                out = torch.full((S, d), float("nan"), dtype=torch.float16, device="cuda")
+                out = outs.setdefault((S, d), torch.empty((S, d), dtype=torch.float16, device="cuda"))
+                out.fill_(float("nan"))
+                torch.cuda.synchronize()
+                dist.barrier()
                 pkg.kernel_status_reset()
-                pkg.run_mode(ctx, pkg.parse_mode(name), w, out, p)
+                for rep in range(2 if reduce == 1 else 1):
+                    pkg.run_mode(ctx, pkg.parse_mode(name), w, out, p)
                 torch.cuda.synchronize()
                 ma, mr = oracle.compare(out.float().cpu().numpy(), ref)
-                good = bool(np.isfinite(ma)) and ma <= 2e-3 and ma <= 1e-2 * mr and pkg.kernel_status()[0] == 0
+                abs_tol = 2e-3
+                if reduce == 0 and world > 2:
+                    # NCCL adds fp16 partials in fp16, one rounding per hop: with more than two ranks the
+                    # absolute gate is two fp16 ulps of the largest output when that is the larger number
+                    # (the fused path accumulates in fp32, rounds once and keeps the plain 2e-3 gate)
+                    abs_tol = max(abs_tol, 2.0 * float(np.spacing(np.float16(mr))))
+                good = bool(np.isfinite(ma)) and ma <= abs_tol and ma <= 1e-2 * mr and pkg.kernel_status()[0] == 0
                 ok &= good
                 print(f"rank {{rank}} S={{S}} d={{d}} split={{split}} causal={{causal}} reduce={{reduce}} {{name}}: max_abs={{ma:.3e}} max_ref={{mr:.3e}} {{'PASS' if good else 'FAIL'}}", flush=True)
     flag = torch.tensor([1 if ok else 0])
@@ -78,3 +95,12 @@ def run_workers(tmp_path, nproc, reduces):
 
 def test_two_ranks_nccl_reduction(tmp_path):
     run_workers(tmp_path, 2, (0,))
+
+
+def test_two_ranks_fused_p2p_reduction(tmp_path):
+    """stream mode with the projection + reduction fused in one persistent kernel over peer memory."""
+    run_workers(tmp_path, 2, (1,))
+
+
+def test_eight_ranks_both_reductions(tmp_path):
+    run_workers(tmp_path, 8, (0, 1))
