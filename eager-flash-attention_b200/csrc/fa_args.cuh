@@ -29,7 +29,8 @@ __device__ __forceinline__ float ex2(float x)
 }
 
 // Warp-specialised two-tile kernel (fa_fwd_ws_sm100.cu), d_h = 64 or 128.
+// reserve_sms > 0: persistent grid that leaves that many SMs without an attention CTA.
 int fa_forward_ws(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FaArgs& a,
-                  int d_h, bool out_f16, cudaStream_t stream);
+                  int d_h, bool out_f16, int reserve_sms, cudaStream_t stream);
 
 }  // namespace efa

@@ -432,7 +432,7 @@ const char* fa_check_params(const efa_flash_params& p, int q_rows)
 
 int fa_forward(const void* Q, const void* K, const void* V, void* O, int o_dtype,
                const efa_flash_partials* part, int q_start, int q_rows,
-               const efa_flash_params& p, cudaStream_t stream, int* tile_counters, int tile_rows)
+               const efa_flash_params& p, cudaStream_t stream, int* tile_counters, int tile_rows, int reserve_sms)
 {
     if (const char* why = fa_check_params(p, q_rows)) { set_error("flash_attn_tc_forward: %s", why); return 2; }
     if (q_start < 0 || q_start % 64 != 0 || q_start + q_rows > p.S) {
@@ -477,7 +477,7 @@ int fa_forward(const void* Q, const void* K, const void* V, void* O, int o_dtype
     // switch, like the reference's --no_prio) keeps them on the one-tile kernel below for A/B timing.
     static const bool one_tile_only = [] { const char* e = getenv("EFA_ATTN_ONE_TILE"); return e && e[0] == '1'; }();
     if ((p.d_h == 64 || p.d_h == 128) && !one_tile_only)
-        return fa_forward_ws(tq, tk, tv, a, p.d_h, f16, stream);
+        return fa_forward_ws(tq, tk, tv, a, p.d_h, f16, reserve_sms, stream);
     dim3 grid(p.H_local * p.split, (q_rows + FA_BM - 1) / FA_BM);
     switch (p.d_h) {
         case 16:  return f16 ? launch_fa<16, true>(tq, tk, tv, a, grid, stream)  : launch_fa<16, false>(tq, tk, tv, a, grid, stream);

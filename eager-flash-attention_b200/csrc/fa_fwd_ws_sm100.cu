@@ -51,12 +51,16 @@ struct WsCfg {
 __device__ __forceinline__ void setmaxnreg_dec_56() { asm volatile("setmaxnreg.dec.sync.aligned.u32 56;"); }
 __device__ __forceinline__ void setmaxnreg_inc_224() { asm volatile("setmaxnreg.inc.sync.aligned.u32 224;"); }
 
-template <int D, bool OUT_F16>
+// PERSIST = false: one work item (256 rows of one head/split) per CTA, grid (H_local*split, row blocks).
+// PERSIST = true: a 1-D grid of fewer CTAs than SMs; each CTA takes work items from a global counter in
+// the same row-major order. The SMs left without a CTA stay free for the projection and the AllReduce
+// of finished tiles, which otherwise can only start when an attention CTA retires.
+template <int D, bool OUT_F16, bool PERSIST>
 __global__ void __launch_bounds__(WS_THREADS, 1)
 fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ,
                  const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV,
-                 const FaArgs a)
+                 const FaArgs a, int* work_counter, int items_x, int items_total)
 {
     using C = WsCfg<D>;
     constexpr uint32_t SWZ = swizzle_code(128);
@@ -76,32 +80,38 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ,
     __shared__ uint32_t tmem_base_smem;
     __shared__ int abort_word;
     __shared__ int half_done[2][2];                       // [tile][64-row half]: warps that finished their stores
+    __shared__ int s_item;
 
     const int tid  = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
 
-    const int head  = blockIdx.x % a.H_local;
-    const int split = blockIdx.x / a.H_local;
-    const int block_row0 = blockIdx.y * (2 * WS_BM);
-    const int rows_valid = min(2 * WS_BM, a.q_rows - block_row0);      // 64, 128, 192 or 256
-    const int kv_lo = split * a.kv_len;
-    const int kv_hi = kv_lo + a.kv_len;
-
-    // Per Q tile: first absolute row, valid rows, number of key stages.
-    int q_abs0[2], rows_q[2], nblk[2];
-    #pragma unroll
-    for (int q = 0; q < 2; q++) {
-        q_abs0[q] = a.q_start + block_row0 + q * WS_BM;
-        rows_q[q] = max(0, min(WS_BM, rows_valid - q * WS_BM));
-        const int kv_end = a.causal ? min(kv_hi, q_abs0[q] + rows_q[q]) : kv_hi;
-        nblk[q] = (rows_q[q] > 0 && kv_end > kv_lo) ? (kv_end - kv_lo + WS_BN - 1) / WS_BN : 0;
-    }
-    const int nblk_max = max(nblk[0], nblk[1]);
-
+    // ---- once per CTA
     if (tid == 0) {
         abort_word = 0;
+        tma_prefetch_desc(&tmQ);
+        tma_prefetch_desc(&tmK);
+        tma_prefetch_desc(&tmV);
+    }
+    if (warp == 9) tmem_alloc(&tmem_base_smem, C::TMEM_COLS);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_base_smem;
+    const int kv_len = a.kv_len;
+
+    struct ItemInfo { int head, split, block_row0, kv_lo, kv_hi, nblk_max; int q_abs0[2], rows_q[2], nblk[2]; };
+    // Next work item. Thread 0 rebuilds the barriers for every item: all threads are past the previous one.
+    // Both role branches below call this the same number of times, so its __syncthreads pair up.
+    auto fetch_item = [&](int round, ItemInfo& it) -> bool {
+    // ---- next work item; barriers are rebuilt for every item (all threads are past the previous one)
+    if (tid == 0) {
+        s_item = PERSIST ? atomicAdd(work_counter, 1) : (int)(blockIdx.y * gridDim.x + blockIdx.x);
         half_done[0][0] = half_done[0][1] = half_done[1][0] = half_done[1][1] = 0;
+        if (round > 0) {
+            for (int q = 0; q < 2; q++) { mbar_inval(&q_full[q]); mbar_inval(&s_full[q]); mbar_inval(&p_full[q]); mbar_inval(&o_done[q]); }
+            for (int s = 0; s < NST; s++) { mbar_inval(&k_full[s]); mbar_inval(&k_empty[s]); mbar_inval(&v_full[s]); mbar_inval(&v_empty[s]); }
+        }
         for (int q = 0; q < 2; q++) {
             mbar_init(&q_full[q], 1);
             mbar_init(&s_full[q], 1);
@@ -113,21 +123,50 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ,
             mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
         }
         mbar_fence_init();
-        tma_prefetch_desc(&tmQ);
-        tma_prefetch_desc(&tmK);
-        tma_prefetch_desc(&tmV);
     }
-    if (warp == 9) tmem_alloc(&tmem_base_smem, C::TMEM_COLS);
-    tc_fence_before_sync();
     __syncthreads();
-    tc_fence_after_sync();
-    const uint32_t tmem_base = tmem_base_smem;
+    const int item = s_item;
+    if (item >= items_total || abort_word != 0) return false;
+
+    const int item_x = item % items_x, item_y = item / items_x;
+    it.head  = item_x % a.H_local;
+    it.split = item_x / a.H_local;
+    it.block_row0 = item_y * (2 * WS_BM);
+    const int rows_valid = min(2 * WS_BM, a.q_rows - it.block_row0);      // 64, 128, 192 or 256
+    it.kv_lo = it.split * kv_len;
+    it.kv_hi = it.kv_lo + kv_len;
+
+    // Per Q tile: first absolute row, valid rows, number of key stages.
+    #pragma unroll
+    for (int q = 0; q < 2; q++) {
+        it.q_abs0[q] = a.q_start + it.block_row0 + q * WS_BM;
+        it.rows_q[q] = max(0, min(WS_BM, rows_valid - q * WS_BM));
+        const int kv_end = a.causal ? min(it.kv_hi, it.q_abs0[q] + it.rows_q[q]) : it.kv_hi;
+        it.nblk[q] = (it.rows_q[q] > 0 && kv_end > it.kv_lo) ? (kv_end - it.kv_lo + WS_BN - 1) / WS_BN : 0;
+    }
+    it.nblk_max = max(it.nblk[0], it.nblk[1]);
+    return true;
+    };
+    auto end_item = [&]() {
+        __syncwarp();
+        tc_fence_before_sync();
+        __syncthreads();
+        tc_fence_after_sync();
+    };
+#define EFA_ITEM_LOCALS \
+    const int head = it.head, split = it.split, block_row0 = it.block_row0, kv_lo = it.kv_lo, kv_hi = it.kv_hi, nblk_max = it.nblk_max; \
+    const int* q_abs0 = it.q_abs0; const int* rows_q = it.rows_q; const int* nblk = it.nblk; \
+    (void)head; (void)split; (void)block_row0; (void)kv_lo; (void)kv_hi; (void)nblk_max; (void)q_abs0; (void)rows_q; (void)nblk;
 
     if (warp >= 8) {
+        setmaxnreg_dec_56();
+        for (int round = 0; ; round++) {
+        ItemInfo it;
+        if (!fetch_item(round, it)) break;
+        EFA_ITEM_LOCALS
         // =====================================================================================
         // Producer / MMA warpgroup
         // =====================================================================================
-        setmaxnreg_dec_56();
         if (warp == 8 && lane == 0) {
             // ---- TMA producer
             auto load_tile = [&](uint8_t* dst, const CUtensorMap* tm, uint64_t* bar, int row) {
@@ -207,12 +246,22 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ,
                 tc_commit(&v_empty[s]);
                 if (j + 1 < nblk_max) tc_commit(&k_empty[(j + 1) % NST]);
             }
+            // The last commit has to land before the barriers are rebuilt for the next work item.
+            if (ok && nblk_max > 0)
+                mbar_wait(&v_empty[(nblk_max - 1) % NST], (uint32_t)(((nblk_max - 1) / NST) & 1), &abort_word, 28);
+        }
+        end_item();
+        if (!PERSIST) break;
         }
     } else {
+        setmaxnreg_inc_224();
+        for (int round = 0; ; round++) {
+        ItemInfo it;
+        if (!fetch_item(round, it)) break;
+        EFA_ITEM_LOCALS
         // =====================================================================================
         // Softmax warpgroups: tile q = warp / 4, row = thread index within the warpgroup
         // =====================================================================================
-        setmaxnreg_inc_224();
         const int q = warp >> 2;
         const int row = tid - q * WS_BM;
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
@@ -374,17 +423,19 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ,
                 }
             }
         }
+        end_item();
+        if (!PERSIST) break;
+        }
     }
-
-    // ---- teardown (every thread of the CTA gets here, whatever happened above)
-    __syncwarp();
-    tc_fence_before_sync();
+#undef EFA_ITEM_LOCALS
     __syncthreads();
+
+    // ---- teardown
     if (abort_word != 0) {
         for (int i = 0; i < 64; i++) __nanosleep(100000);
         if (tid == 0 && a.status != nullptr) {
             if (atomicCAS(a.status, 0, (int)KS_WAIT_TIMEOUT) == 0) {
-                a.status[1] = (int)(blockIdx.y * gridDim.x + blockIdx.x);
+                a.status[1] = s_item;
                 a.status[2] = abort_word;
             }
         }
@@ -393,19 +444,35 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ,
     if (warp == 9) tmem_dealloc(tmem_base, C::TMEM_COLS);
 }
 
-template <int D, bool OUT_F16>
+template <int D, bool OUT_F16, bool PERSIST>
 int launch_ws(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FaArgs& args,
-              dim3 grid, cudaStream_t stream)
+              int reserve_sms, cudaStream_t stream)
 {
     using C = WsCfg<D>;
     static bool configured[64] = {};
     int dev = 0;
     EFA_CUDA(cudaGetDevice(&dev));
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-        EFA_CUDA(cudaFuncSetAttribute(fa_fwd_ws_kernel<D, OUT_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+        EFA_CUDA(cudaFuncSetAttribute(fa_fwd_ws_kernel<D, OUT_F16, PERSIST>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
         configured[dev] = true;
     }
-    fa_fwd_ws_kernel<D, OUT_F16><<<grid, WS_THREADS, C::SMEM_BYTES, stream>>>(tq, tk, tv, args);
+    const int items_x = args.H_local * args.nsplit;
+    const int items_y = (args.q_rows + 2 * WS_BM - 1) / (2 * WS_BM);
+    const int total = items_x * items_y;
+    if (PERSIST) {
+        int sms = 148;
+        EFA_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        int ctas = sms - reserve_sms;
+        if (ctas < 1) ctas = 1;
+        if (ctas > total) ctas = total;
+        int* counter = work_counter_slot();
+        if (!counter) { set_error("no device memory for the work counter"); return 1; }
+        EFA_CUDA(cudaMemsetAsync(counter, 0, sizeof(int), stream));
+        fa_fwd_ws_kernel<D, OUT_F16, true><<<ctas, WS_THREADS, C::SMEM_BYTES, stream>>>(tq, tk, tv, args, counter, items_x, total);
+    } else {
+        dim3 grid(items_x, items_y);
+        fa_fwd_ws_kernel<D, OUT_F16, false><<<grid, WS_THREADS, C::SMEM_BYTES, stream>>>(tq, tk, tv, args, nullptr, items_x, total);
+    }
     EFA_CUDA(cudaGetLastError());
     return 0;
 }
@@ -413,12 +480,19 @@ int launch_ws(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& t
 }  // namespace
 
 // Launch of the warp-specialised kernel; the caller has validated the arguments and built the maps.
+// reserve_sms > 0 selects the persistent form with that many SMs left free.
 int fa_forward_ws(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FaArgs& a,
-                  int d_h, bool out_f16, cudaStream_t stream)
+                  int d_h, bool out_f16, int reserve_sms, cudaStream_t stream)
 {
-    dim3 grid(a.H_local * a.nsplit, (a.q_rows + 2 * WS_BM - 1) / (2 * WS_BM));
-    if (d_h == 64)  return out_f16 ? launch_ws<64, true>(tq, tk, tv, a, grid, stream)  : launch_ws<64, false>(tq, tk, tv, a, grid, stream);
-    if (d_h == 128) return out_f16 ? launch_ws<128, true>(tq, tk, tv, a, grid, stream) : launch_ws<128, false>(tq, tk, tv, a, grid, stream);
+    const bool persist = reserve_sms > 0;
+    if (d_h == 64) {
+        if (persist) return out_f16 ? launch_ws<64, true, true>(tq, tk, tv, a, reserve_sms, stream) : launch_ws<64, false, true>(tq, tk, tv, a, reserve_sms, stream);
+        return out_f16 ? launch_ws<64, true, false>(tq, tk, tv, a, 0, stream) : launch_ws<64, false, false>(tq, tk, tv, a, 0, stream);
+    }
+    if (d_h == 128) {
+        if (persist) return out_f16 ? launch_ws<128, true, true>(tq, tk, tv, a, reserve_sms, stream) : launch_ws<128, false, true>(tq, tk, tv, a, reserve_sms, stream);
+        return out_f16 ? launch_ws<128, true, false>(tq, tk, tv, a, 0, stream) : launch_ws<128, false, false>(tq, tk, tv, a, 0, stream);
+    }
     set_error("fa_forward_ws: d_h=%d is not handled by the warp-specialised kernel", d_h);
     return 2;
 }

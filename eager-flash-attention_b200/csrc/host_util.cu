@@ -111,6 +111,23 @@ int* kernel_status_word()
     return words[dev];
 }
 
+int* work_counter_slot()
+{
+    constexpr int kMaxDev = 64, kSlots = 256;
+    static int* ring[kMaxDev] = {};
+    static unsigned next[kMaxDev] = {};
+    static std::mutex mu;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return nullptr;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!ring[dev]) {
+        int* p = nullptr;
+        if (cudaMalloc(&p, kSlots * sizeof(int)) != cudaSuccess) return nullptr;
+        ring[dev] = p;
+    }
+    return ring[dev] + (next[dev]++ % kSlots);
+}
+
 int make_tmap_f16(CUtensorMap* out, const void* base, int rank,
                   const unsigned long long* dims, const unsigned long long* strides_bytes,
                   const unsigned* box)

@@ -37,6 +37,10 @@ const DriverApi* driver_api();
 // Device-side status word (int[4]) of the current device, allocated on first use.
 int* kernel_status_word();
 
+// A device int for one launch (work distribution of persistent kernels): slots of a small per-device
+// ring handed out round-robin; the caller clears its slot on the launch stream.
+int* work_counter_slot();
+
 // fp16 tensor map over a row-major tensor viewed as up to 3 dimensions (dim 0 fastest).
 // `box` rows x `box_cols` columns, swizzle chosen from box_cols * 2 bytes (32, 64 or 128).
 int make_tmap_f16(CUtensorMap* out, const void* base, int rank,

@@ -39,11 +39,12 @@ struct Run {
     }
 
     // Attention kernel only (launch_attention_raw, attn_main.cu:234-245).
-    int attention_raw(__half* O, int ws_rows, int q_start, int q_rows, cudaStream_t s, int* counters, int tile_rows)
+    int attention_raw(__half* O, int ws_rows, int q_start, int q_rows, cudaStream_t s, int* counters, int tile_rows,
+                      int reserve_sms = 0)
     {
         efa_flash_partials q = ws(ws_rows);
         launches++;
-        return fa_forward(w.Qh, w.Kh, w.Vh, O, EFA_F16, &q, q_start, q_rows, p.flash_tc, s, counters, tile_rows);
+        return fa_forward(w.Qh, w.Kh, w.Vh, O, EFA_F16, &q, q_start, q_rows, p.flash_tc, s, counters, tile_rows, reserve_sms);
     }
     // launch_combine (attn_main.cu:247-252): no-op when split == 1.
     int combine(__half* O, int ws_rows, int row0, int rows, cudaStream_t s)
@@ -302,8 +303,13 @@ int run_stream(Run& r, __half* output, efa_run_stats* st)
 
     EFA_CUDA(cudaMemsetAsync(counters, 0, (size_t)p.num_tiles * sizeof(int), c->compute_stream));
     EFA_CUDA(cudaEventRecord(reset_done, c->compute_stream));
+    // With more than one rank the attention grid leaves a few SMs without a CTA, so that the projection
+    // and the AllReduce of finished tiles find an SM at once instead of waiting for an attention CTA to
+    // retire (the SM-contention problem of this schedule). EFA_RESERVE_SMS overrides the number.
+    int reserve = (p.R > 1 && !p.skip_comm) ? 16 : 0;
+    if (const char* e = getenv("EFA_RESERVE_SMS")) reserve = atoi(e);
     EFA_CUDA(cudaEventRecord(c->ev_t0, c->compute_stream));
-    if (r.attention_raw(O_all, p.S, 0, p.S, c->compute_stream, counters, p.tile)) return 1;
+    if (r.attention_raw(O_all, p.S, 0, p.S, c->compute_stream, counters, p.tile, reserve)) return 1;
     EFA_CUDA(cudaEventRecord(c->ev_t1, c->compute_stream));
 
     EFA_CUDA(cudaStreamWaitEvent(c->proj_stream, reset_done, 0));   // never observe a stale counter

@@ -133,3 +133,28 @@ def test_stream_mode_with_the_fused_projection_kernel_single_rank(pkg, oracle, t
         assert st.kernel_launches == 2
         got = out.float().cpu().numpy()
         assert_close(oracle, got if rows is None else got[rows], ref, f"rep {rep}")
+
+
+@pytest.mark.parametrize("case", [(1024, 512, 8, 128, 1, 1), (2048, 1024, 8, 256, 0, 1), (4096, 1024, 16, 128, 1, 1), (2048, 512, 8, 128, 1, 2)],
+                         ids=lambda c: "S%d_d%d_H%d_t%d_c%d_s%d" % c)
+def test_stream_mode_with_reserved_sms(pkg, oracle, torch_cuda, ctx, case, monkeypatch):
+    """The persistent form of the attention kernel (used with more than one rank): fewer CTAs than SMs,
+    work items taken from a global counter in row order, barriers rebuilt per item. EFA_RESERVE_SMS forces
+    it on one rank; 100 reserved SMs leave 48 CTAs, so every CTA processes several items."""
+    torch = torch_cuda
+    S, d, H, tile, causal, split = case
+    monkeypatch.setenv("EFA_RESERVE_SMS", "100")
+    p = pkg.make_params(S, d, H, tile, 2, split, causal)
+    bits, vals = ref_inputs_f16(oracle, S, d, H, 1, 0, 42) if S <= 2048 else normal_inputs_f16(pkg, oracle, p, 0, 42)
+    rows = None if S <= 2048 else np.arange(0, S, 13, dtype=np.int32)
+    ref = oracle.block_rows([vals], d, causal, rows)
+    dev = to_dev(torch, bits)
+    w = pkg.Weights(*(t.data_ptr() for t in dev))
+    for rep in range(2):
+        out = torch.full((S, d), float("nan"), dtype=torch.float16, device="cuda")
+        pkg.kernel_status_reset()
+        pkg.run_mode(ctx, pkg.MODE_STREAM, w, out, p)
+        torch.cuda.synchronize()
+        assert pkg.kernel_status()[0] == 0, pkg.kernel_status()
+        got = out.float().cpu().numpy()
+        assert_close(oracle, got if rows is None else got[rows], ref, f"rep {rep}")

@@ -29,7 +29,7 @@ WORKER = textwrap.dedent("""
     ok = True
     outs = {{}}
     if world > 2:
-        cases = [(1024, 1024, 8, 128, 2, 1, 1), (2048, 2048, 16, 256, 2, 1, 0), (1024, 512, 8, 256, 2, 1, 0), (960, 1024, 8, 64, 3, 1, 1)]
+        cases = [(1024, 1024, 8, 128, 2, 1, 1), (960, 1024, 8, 64, 3, 1, 1)]
     for S, d, H, tile, nbuf, split, causal in cases:
         if H % world != 0:
             continue
@@ -84,7 +84,7 @@ def run_workers(tmp_path, nproc, reduces):
     script = tmp_path / "worker.py"
     script.write_text(WORKER.format(root=ROOT, reduces=reduces))
     port = 29600 + (os.getpid() % 1000)
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", OMP_NUM_THREADS="4")
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
                         "--master-addr", "127.0.0.1", "--master-port", str(port), str(script)],
                        capture_output=True, text=True, timeout=1500, env=env)
