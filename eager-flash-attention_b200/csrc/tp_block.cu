@@ -303,10 +303,12 @@ int run_stream(Run& r, __half* output, efa_run_stats* st)
 
     EFA_CUDA(cudaMemsetAsync(counters, 0, (size_t)p.num_tiles * sizeof(int), c->compute_stream));
     EFA_CUDA(cudaEventRecord(reset_done, c->compute_stream));
-    // With more than one rank the attention grid leaves a few SMs without a CTA, so that the projection
-    // and the AllReduce of finished tiles find an SM at once instead of waiting for an attention CTA to
-    // retire (the SM-contention problem of this schedule). EFA_RESERVE_SMS overrides the number.
-    int reserve = (p.R > 1 && !p.skip_comm) ? 16 : 0;
+    // EFA_RESERVE_SMS = k runs the attention kernel in its persistent form on (SMs - k) CTAs, so that the
+    // projection and the AllReduce of finished tiles always find an SM. Measured on 8xB200 (benchmark
+    // shape) this loses: the projection of a group is then confined to the k reserved SMs, while with the
+    // plain grid its CTAs (higher stream priority) spread over every SM an attention CTA retires from.
+    // Default off.
+    int reserve = 0;
     if (const char* e = getenv("EFA_RESERVE_SMS")) reserve = atoi(e);
     EFA_CUDA(cudaEventRecord(c->ev_t0, c->compute_stream));
     if (r.attention_raw(O_all, p.S, 0, p.S, c->compute_stream, counters, p.tile, reserve)) return 1;
@@ -318,12 +320,21 @@ int run_stream(Run& r, __half* output, efa_run_stats* st)
     // reference's schedule. Small tiles make one launch and one collective per tile cost more than the
     // attention of the tile (a 128-row tile of the benchmark shape is a few microseconds of attention on
     // eight GPUs), so the default groups about S/8 rows.
+    // Automatic grouping: S/8 rows per group, except that the last eighth of the rows is cut into
+    // S/16, S/32 and S/32: what is still exposed after the attention kernel ends is the projection and
+    // the collective of the last group, so that one should be small.
+    const bool auto_groups = p.group_tiles <= 0;
     int gt = p.group_tiles;
-    if (gt <= 0) { gt = (p.S / 8) / p.tile; if (gt < 1) gt = 1; }
+    if (auto_groups) { gt = (p.S / 8) / p.tile; if (gt < 1) gt = 1; }
     if (gt > p.num_tiles) gt = p.num_tiles;
     int gidx = 0;
-    for (int t0g = 0; t0g < p.num_tiles; t0g += gt, gidx++) {
-        const int nt = (t0g + gt <= p.num_tiles) ? gt : p.num_tiles - t0g;
+    for (int t0g = 0; t0g < p.num_tiles; gidx++) {
+        int nt = (t0g + gt <= p.num_tiles) ? gt : p.num_tiles - t0g;
+        if (auto_groups && gt >= 4 && t0g + gt >= p.num_tiles) {
+            const int left = p.num_tiles - t0g;          // tiles of the last eighth still to place
+            nt = (left > gt / 2) ? gt / 2 : (left > gt / 4 ? left - gt / 4 : left);
+            if (nt < 1) nt = left;
+        }
         for (int t = t0g; t < t0g + nt; t++)
             EFA_CU(api->cuStreamWaitValue32((CUstream)c->proj_stream, (CUdeviceptr)(counters + t),
                                             (cuuint32_t)target, CU_STREAM_WAIT_VALUE_GEQ));
@@ -336,6 +347,7 @@ int run_stream(Run& r, __half* output, efa_run_stats* st)
         const int slot = gidx % c->ncomm;
         EFA_CUDA(cudaStreamWaitEvent(c->comm_streams[slot], c->events[gidx], 0));
         if (r.allreduce(slot, S_t, output + (size_t)t0g * p.tile * p.d, (size_t)rows * p.d)) return 1;
+        t0g += nt;
     }
     if (sync_stream(c, c->compute_stream, counters, p.num_tiles)) return 1;
     if (sync_stream(c, c->proj_stream, counters, p.num_tiles)) return 1;

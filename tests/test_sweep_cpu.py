@@ -1,0 +1,60 @@
+"""The sweep / table / cost-model tooling on synthetic CSV rows (no GPU)."""
+import os
+import subprocess
+import sys
+
+from conftest import ROOT
+
+SWEEP = os.path.join(ROOT, "eager-flash-attention_b200", "sweep")
+HEADER = "S,H,d_h,causal,R,kernel,tile,nbuf,split,ncomm,proj,mode,min_ms,max_ms,mean_ms,median_ms,std_ms,tokens_per_s,attn_kernel_ms,reduce,data"
+
+
+def write_csv(path, rows, header=HEADER):
+    with open(path, "w") as f:
+        f.write(header + "\n")
+        for r in rows:
+            f.write(",".join(str(x) for x in r) + "\n")
+
+
+def test_cost_model_recovers_alpha_and_beta(tmp_path):
+    sys.path.insert(0, SWEEP)
+    import cost_model
+    alpha, beta = 0.02, 5e8            # 20 us, 500 GB/s expressed in bytes per ms
+    rows = []
+    for tile in (128, 512, 2048, 8192):
+        n = 16384 // tile
+        t = n * (alpha + tile * 1024 * 2 / beta)
+        rows.append((16384, 16, 64, 0, 8, "tc", tile, 2, 1, 1, "fp16", "comm", t, t, t, t, 0, 0, 0, "nccl", "normal"))
+    p = tmp_path / "comm.csv"
+    write_csv(p, rows)
+    a, b = cost_model.fit_allreduce(cost_model.read_rows(str(p)), 2)
+    assert abs(a - alpha) < 1e-9 and abs(b - beta) / beta < 1e-9
+    meg, st = cost_model.predict(16384, 1024, 1024, 4, 1.0, 0.1, a, b, 2)
+    assert abs(meg - (1.0 + 0.1 + alpha + 16384 * 1024 * 2 / beta)) < 1e-9
+    assert st >= 1.0
+
+
+def test_tables_accept_reference_rows_without_the_new_columns(tmp_path):
+    ours = tmp_path / "ours.csv"
+    ref = tmp_path / "ref.csv"
+    base = (16384, 16, 64, 0, 8, "tc", 128, 2, 1, 4, "fp16")
+    write_csv(ours, [base + ("attn", 1, 1, 1, 0.25, 0, 0, 0, "nccl", "normal"),
+                     base + ("megatron", 1, 1, 1, 0.45, 0, 0, 0, "nccl", "normal"),
+                     base + ("stream", 1, 1, 1, 0.40, 0, 0, 0, "nccl", "normal")])
+    ref_header = ",".join(HEADER.split(",")[:17])
+    write_csv(ref, [base[:10] + ("fp32", "megatron", 1, 1, 1, 1.05, 0), base[:10] + ("fp32", "stream", 1, 1, 1, 2.4, 0)], ref_header)
+    r = subprocess.run([sys.executable, os.path.join(SWEEP, "bench_tables.py"), str(ours), str(ref)], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    assert "1.12x" in r.stdout           # megatron / stream = 0.45 / 0.40
+    assert "| stream | 2.400 | 0.400 | 6.00x |" in r.stdout
+
+
+def test_sweep_dry_run_lists_the_reference_suites():
+    r = subprocess.run([sys.executable, os.path.join(SWEEP, "bench_sweep.py"), "--ranks", "8",
+                        "--suite", "core,causal,kernel,modes,scaling,model,comm,tiles", "--dry-run"],
+                       capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    lines = [l for l in r.stdout.splitlines() if "attn_bench" in l]
+    assert len(lines) > 40
+    assert all("efa_launch -n 8" in l for l in lines)
+    assert any("--modes comm" in l for l in lines) and any("--causal" in l for l in lines)
