@@ -206,9 +206,9 @@ def main():
     if why:
         raise SystemExit(f"invalid workload for {world_size} ranks: {why}")
     if args.reduce == "auto":
-        # Measured on 8xB200 for this workload: the fused kernel wins with one or two ranks, grouped NCCL
-        # AllReduces with four and eight (profiles/ has the table).
-        args.reduce = "p2p" if world_size <= 2 else "nccl"
+        # Measured on 1, 2, 4 and 8 B200s for this workload: grouped NCCL AllReduces are as fast as or faster
+        # than the fused peer-memory kernel at every rank count (profiles/stream_modes_C5.md has the table).
+        args.reduce = "nccl"
     p.reduce = pkg.REDUCE_P2P if args.reduce == "p2p" else pkg.REDUCE_NCCL
     p.group_tiles = args.group_tiles
     mode = pkg.parse_mode(args.mode)
@@ -315,7 +315,7 @@ def main():
             tokens_per_s=p.S / (ms * 1e-3),
             modes_ms=modes, exposed_comm_frac=exposed,
             block_roofline=dict(t_ms=t_roof, frac=t_roof / ms, peak=f"{pk['tflops']} TFLOP/s bf16 {pk['source']}; 770 GB/s NVLink measured"),
-            roofline=dict(bound="tensor", kernel="fa_fwd_kernel<128>", achieved=achieved, peak=pk["tflops"], unit="TFLOP/s",
+            roofline=dict(bound="tensor", kernel="fa_fwd_ws_kernel<128>", achieved=achieved, peak=pk["tflops"], unit="TFLOP/s",
                           frac=achieved / pk["tflops"], peak_source=f"of {pk['source']} (burst bf16)",
                           frac_sustained=achieved / pk["tflops_sustained"], attn_kernel_ms=attn_ms,
                           algorithmic_flops=fl, traffic=None),

@@ -48,6 +48,13 @@ struct WsCfg {
     static constexpr int TMEM_COLS  = 512;
 };
 
+__device__ __forceinline__ float max3(float a, float b, float c)
+{
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+
 __device__ __forceinline__ void setmaxnreg_dec_56() { asm volatile("setmaxnreg.dec.sync.aligned.u32 56;"); }
 __device__ __forceinline__ void setmaxnreg_inc_224() { asm volatile("setmaxnreg.inc.sync.aligned.u32 224;"); }
 
@@ -76,7 +83,7 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ,
 
     __shared__ __align__(8) uint64_t q_full[2];
     __shared__ __align__(8) uint64_t k_full[NST], k_empty[NST], v_full[NST], v_empty[NST];
-    __shared__ __align__(8) uint64_t s_full[2], p_full[2], o_done[2];
+    __shared__ __align__(8) uint64_t s_full[2], p_full[2][2], o_done[2];
     __shared__ uint32_t tmem_base_smem;
     __shared__ int abort_word;
     __shared__ int half_done[2][2];                       // [tile][64-row half]: warps that finished their stores
@@ -109,13 +116,14 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ,
         s_item = PERSIST ? atomicAdd(work_counter, 1) : (int)(blockIdx.y * gridDim.x + blockIdx.x);
         half_done[0][0] = half_done[0][1] = half_done[1][0] = half_done[1][1] = 0;
         if (round > 0) {
-            for (int q = 0; q < 2; q++) { mbar_inval(&q_full[q]); mbar_inval(&s_full[q]); mbar_inval(&p_full[q]); mbar_inval(&o_done[q]); }
+            for (int q = 0; q < 2; q++) { mbar_inval(&q_full[q]); mbar_inval(&s_full[q]); mbar_inval(&p_full[q][0]); mbar_inval(&p_full[q][1]); mbar_inval(&o_done[q]); }
             for (int s = 0; s < NST; s++) { mbar_inval(&k_full[s]); mbar_inval(&k_empty[s]); mbar_inval(&v_full[s]); mbar_inval(&v_empty[s]); }
         }
         for (int q = 0; q < 2; q++) {
             mbar_init(&q_full[q], 1);
             mbar_init(&s_full[q], 1);
-            mbar_init(&p_full[q], WS_BM);
+            mbar_init(&p_full[q][0], WS_BM);
+            mbar_init(&p_full[q][1], WS_BM);
             mbar_init(&o_done[q], 1);
         }
         for (int s = 0; s < NST; s++) {
@@ -196,10 +204,10 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ,
                               IDESC_QK, ks > 0 ? 1u : 0u);
                 }
             };
-            auto issue_pv = [&](int q, int stage, bool first) {
+            auto issue_pv = [&](int q, int stage, bool first, int half) {
                 const uint32_t va = smem_u32(sV + stage * C::TILE_BYTES);
                 #pragma unroll
-                for (int ks = 0; ks < WS_BN / 16; ks++)
+                for (int ks = half * 4; ks < half * 4 + 4; ks++)
                     tc_mma_ts(tmem_base + 256 + q * 128, tmem_base + q * 128 + ks * 8,
                               smem_desc(va + ks * 16 * 128, C::BOX_BYTES, 1024, SWZ), IDESC_PV, (!first || ks > 0) ? 1u : 0u);
             };
@@ -224,10 +232,14 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ,
                 bool k_next_ready = false;
                 for (int q = 0; q < 2 && ok; q++) {
                     if (j >= nblk[q]) continue;
-                    ok = mbar_wait(&p_full[q], (uint32_t)(j & 1), &abort_word, 26);
+                    ok = mbar_wait(&p_full[q][0], (uint32_t)(j & 1), &abort_word, 26);
                     if (!ok) break;
                     tc_fence_after_sync();
-                    issue_pv(q, s, j == 0);
+                    issue_pv(q, s, j == 0, 0);
+                    ok = mbar_wait(&p_full[q][1], (uint32_t)(j & 1), &abort_word, 29);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    issue_pv(q, s, j == 0, 1);
                     if (j + 1 < nblk[q]) {
                         const int ns = (j + 1) % NST;
                         if (!k_next_ready) {
@@ -298,13 +310,14 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ,
                         if (c * 32 + i > lim) su[c][i] = 0xff800000u;
             }
 
+            // row maximum: four independent chains of three-input max (half the instructions of fmaxf)
             float mx0 = kNegInfW, mx1 = kNegInfW, mx2 = kNegInfW, mx3 = kNegInfW;
             #pragma unroll
-            for (int i = 0; i < 32; i++) {
-                mx0 = fmaxf(mx0, __uint_as_float(su[0][i]));
-                mx1 = fmaxf(mx1, __uint_as_float(su[1][i]));
-                mx2 = fmaxf(mx2, __uint_as_float(su[2][i]));
-                mx3 = fmaxf(mx3, __uint_as_float(su[3][i]));
+            for (int i = 0; i < 32; i += 2) {
+                mx0 = max3(mx0, __uint_as_float(su[0][i]), __uint_as_float(su[0][i + 1]));
+                mx1 = max3(mx1, __uint_as_float(su[1][i]), __uint_as_float(su[1][i + 1]));
+                mx2 = max3(mx2, __uint_as_float(su[2][i]), __uint_as_float(su[2][i + 1]));
+                mx3 = max3(mx3, __uint_as_float(su[3][i]), __uint_as_float(su[3][i + 1]));
             }
             const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
             m_true = fmaxf(m_true, mx * a.scale_log2e);
@@ -319,6 +332,22 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ,
             }
             const float m_off = (m_ref == kNegInfW) ? 0.f : m_ref;
 
+            // S(j) complete implies PV(j-1) of this tile complete (the tensor pipe runs in order), and no
+            // part of PV(j) is issued before this thread's first arrival below: O may be rescaled here.
+            if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+                #pragma unroll
+                for (int c = 0; c < D / 32; c++) {
+                    uint32_t o[32];
+                    tmem_ld32(tmem_O + c * 32, o);
+                    tmem_wait_ld();
+                    #pragma unroll
+                    for (int i = 0; i < 32; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                    tmem_st32(tmem_O + c * 32, o);
+                }
+            }
+
+            // P is handed to the MMA warp in two halves of 64 keys: the first four k-steps of P*V run on
+            // the tensor pipe while the exponentials of the second half are still being computed.
             float ps0 = 0.f, ps1 = 0.f;
             #pragma unroll
             for (int c = 0; c < 4; c++) {
@@ -332,25 +361,13 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ,
                     pk[i] = pack_f16x2(p0, p1);
                 }
                 tmem_st16(tmem_S + c * 16, pk);
-            }
-            l_run = l_run * alpha + (ps0 + ps1);
-
-            // S(j) complete implies PV(j-1) of this tile complete (the tensor pipe runs in order), and
-            // PV(j) is not issued before this thread arrives below: O may be rescaled here.
-            if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-                #pragma unroll
-                for (int c = 0; c < D / 32; c++) {
-                    uint32_t o[32];
-                    tmem_ld32(tmem_O + c * 32, o);
-                    tmem_wait_ld();
-                    #pragma unroll
-                    for (int i = 0; i < 32; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                    tmem_st32(tmem_O + c * 32, o);
+                if (c == 1 || c == 3) {
+                    tmem_wait_st();
+                    tc_fence_before_sync();
+                    mbar_arrive(&p_full[q][c >> 1]);
                 }
             }
-            tmem_wait_st();
-            tc_fence_before_sync();
-            mbar_arrive(&p_full[q]);
+            l_run = l_run * alpha + (ps0 + ps1);
         }
 
         if (ok && my_nblk > 0) {
