@@ -13,8 +13,10 @@
 //   REDUCE item (rb, m): the owner waits for R arrivals, sums the R staged partials in fp32, rounds once
 //                        to fp16 and stores the result into every rank's output (peer stores), then
 //                        increments every rank's done flag for row block rb.
-// Each CTA interleaves its GEMM items with the REDUCE items that are LAG row blocks behind, so that
-// a rank never waits for a peer's partial while it still has projections of its own to issue.
+// GEMM items come in groups (all column blocks one rank owns, for one row block) with one signal per
+// group: a system-scope fence costs a round trip, so it is paid per group, not per tile. REDUCE work
+// runs on four warps of its own, so a rank never holds back its projections while it waits for a
+// peer's partial, and the projection side never waits on a peer at all.
 // Flags and tile counters are never reset: targets grow with an epoch number that is the same on all
 // ranks (runs are collective and separated by a host barrier), which removes the reset race between
 // a rank that starts early and a peer that still clears its flags.
