@@ -90,6 +90,7 @@ _SIGNATURES = {
     "efa_flash_attn_tc_check_params": (C.c_char_p, [C.POINTER(FlashParams), C.c_int]),
     "efa_convert_f32_to_f16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "efa_project_f16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "efa_compute_qkv_f16": (C.c_int, [C.c_void_p] * 7 + [C.c_int] * 4 + [C.c_void_p]),
     "efa_kernel_status": (C.c_int, [C.POINTER(C.c_int)]),
     "efa_kernel_status_reset": (C.c_int, []),
     "efa_mode_name": (C.c_char_p, [C.c_int]),
@@ -235,6 +236,12 @@ def convert_f32_to_f16(src, dst, n: int, stream=None) -> None:
 def project(O_tile, W_O, out, rows: int, d_local: int, d: int, stream=None) -> None:
     """project (attn_main.cu:262-273) on fp16 data: out[rows][d] = O_tile[rows][d_local] @ W_O[d_local][d]."""
     _check(lib().efa_project_f16(_ptr(O_tile), _ptr(W_O), _ptr(out), rows, d_local, d, _stream(stream)), "project")
+
+
+def compute_qkv(X, W_q, W_k, W_v, Qh, Kh, Vh, S: int, d: int, H_local: int, d_h: int, stream=None) -> None:
+    """compute_qkv (attn_main.cu:127-153) on fp16 data: Q/K/V = X @ W per head, written fp16 head-major."""
+    _check(lib().efa_compute_qkv_f16(_ptr(X), _ptr(W_q), _ptr(W_k), _ptr(W_v), _ptr(Qh), _ptr(Kh), _ptr(Vh),
+                                     S, d, H_local, d_h, _stream(stream)), "compute_qkv")
 
 
 def kernel_status() -> Sequence[int]:

@@ -3,6 +3,8 @@
 #include "host_util.h"
 #include "runtime.h"
 
+#include <cuda_fp16.h>
+
 #include <chrono>
 #include <cstring>
 
@@ -53,6 +55,21 @@ extern "C" int efa_project_f16(const void* O_tile, const void* W_O, void* out, i
     return project_f16(O_tile, W_O, out, rows, d_local, d, (cudaStream_t)stream);
 }
 
+extern "C" int efa_compute_qkv_f16(const void* X, const void* W_q, const void* W_k, const void* W_v,
+                                   void* Qh, void* Kh, void* Vh, int S, int d, int H_local, int d_h, void* stream)
+{
+    if (!X || !W_q || !W_k || !W_v || !Qh || !Kh || !Vh) { set_error("efa_compute_qkv_f16: null argument"); return 2; }
+    if (d_h != 64 && d_h != 128) { set_error("efa_compute_qkv_f16: d_h must be 64 or 128 (got %d)", d_h); return 2; }
+    if (H_local < 1) { set_error("efa_compute_qkv_f16: H_local must be positive"); return 2; }
+    const __half* W[3] = {static_cast<const __half*>(W_q), static_cast<const __half*>(W_k), static_cast<const __half*>(W_v)};
+    __half* out[3] = {static_cast<__half*>(Qh), static_cast<__half*>(Kh), static_cast<__half*>(Vh)};
+    for (int h = 0; h < H_local; h++)
+        for (int t = 0; t < 3; t++)
+            if (int rc = project_f16(X, W[t] + (size_t)h * d * d_h, out[t] + (size_t)h * S * d_h, S, d, d_h, (cudaStream_t)stream))
+                return rc;
+    return 0;
+}
+
 extern "C" int efa_kernel_status(int* out4)
 {
     if (!out4) { set_error("efa_kernel_status: null argument"); return 2; }
@@ -90,6 +107,11 @@ extern "C" int efa_run_mode_host(efa_ctx* c, int mode,
         if (ensure_bytes(&c->h_Q, &a, qkv) || ensure_bytes(&c->h_K, &b, qkv) || ensure_bytes(&c->h_V, &d, qkv)) return 1;
         c->h_qkv_bytes = a < b ? (a < d ? a : d) : (b < d ? b : d);
         if (ensure_bytes(&c->h_W, &c->h_w_bytes, wb) || ensure_bytes(&c->h_out, &c->h_out_bytes, ob)) return 1;
+    }
+    if (mode == EFA_MODE_STREAM && p->causal && p->split == 1 && !p->skip_proj && p->reduce == EFA_REDUCE_NCCL) {
+        // copy-in, compute and copy-out overlap chunk by chunk
+        efa_weights dev{c->h_Q, c->h_K, c->h_V, c->h_W};
+        return run_stream_host_pipelined(c, Qh, Kh, Vh, W_O, output, dev, c->h_out, *p, stats);
     }
     if (world_barrier(c->world)) return 1;
     const auto t0 = std::chrono::steady_clock::now();

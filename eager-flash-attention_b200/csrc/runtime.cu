@@ -290,6 +290,8 @@ extern "C" int efa_destroy_ctx(efa_ctx* c)
         if (c->nccls[i] && nccl_api()) nccl_api()->CommDestroy(c->nccls[i]);
         if (c->comm_streams[i]) cudaStreamDestroy(c->comm_streams[i]);
     }
+    if (c->h2d_stream) cudaStreamDestroy(c->h2d_stream);
+    if (c->d2h_stream) cudaStreamDestroy(c->d2h_stream);
     if (c->compute_stream) cudaStreamDestroy(c->compute_stream);
     if (c->proj_stream) cudaStreamDestroy(c->proj_stream);
     for (cudaEvent_t e : c->events) cudaEventDestroy(e);

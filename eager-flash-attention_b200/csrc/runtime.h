@@ -33,6 +33,8 @@ struct efa_ctx {
     void* h_Q = nullptr; void* h_K = nullptr; void* h_V = nullptr; void* h_W = nullptr; void* h_out = nullptr;
     size_t h_qkv_bytes = 0, h_w_bytes = 0, h_out_bytes = 0;
 
+    cudaStream_t h2d_stream = nullptr, d2h_stream = nullptr;   // copies of the pipelined host-buffer path
+
     P2PState* p2p = nullptr;
 };
 
@@ -46,5 +48,11 @@ int ensure_bytes(void** ptr, size_t* have, size_t want);
 int ensure_events(efa_ctx* c, size_t n);
 
 int run_mode_impl(efa_ctx* c, int mode, const efa_weights& w, void* output, const efa_params& p, efa_run_stats* stats);
+
+// Stream mode on HOST buffers as a pipeline over row chunks (causal, split == 1): the copy-in of chunk c+1,
+// the attention / projection / AllReduce of chunk c and the copy-out of chunk c-1 overlap. `dev` holds the
+// device staging of Q, K, V, W_O; `dev_out` the device output. Returns 0 and fills stats->wall_ms (max over ranks).
+int run_stream_host_pipelined(efa_ctx* c, const uint16_t* Qh, const uint16_t* Kh, const uint16_t* Vh, const uint16_t* W_O,
+                              uint16_t* host_out, const efa_weights& dev, void* dev_out, const efa_params& p, efa_run_stats* stats);
 
 }  // namespace efa

@@ -373,6 +373,77 @@ int run_comm_only(Run& r, __half* output, efa_run_stats* st)
 
 }  // namespace
 
+int run_stream_host_pipelined(efa_ctx* c, const uint16_t* Qh, const uint16_t* Kh, const uint16_t* Vh, const uint16_t* W_O,
+                              uint16_t* host_out, const efa_weights& dev, void* dev_out, const efa_params& p, efa_run_stats* stats)
+{
+    const DriverApi* api = driver_api();
+    if (!api) return 1;
+    if (!p.causal || p.split != 1 || p.skip_proj) { set_error("pipelined host path: causal, split == 1 only"); return 2; }
+    if (!c->h2d_stream) EFA_CUDA(cudaStreamCreateWithFlags(&c->h2d_stream, cudaStreamNonBlocking));
+    if (!c->d2h_stream) EFA_CUDA(cudaStreamCreateWithFlags(&c->d2h_stream, cudaStreamNonBlocking));
+    // chunks of about S/8 rows, whole tiles
+    int ct = (p.S / 8) / p.tile; if (ct < 1) ct = 1;
+    const int nchunk = (p.num_tiles + ct - 1) / ct;
+    if (scratch(c, p, p.S, p.S, p.num_tiles, 0, (size_t)3 * nchunk + 2)) return 1;
+    Run r{c, dev, p};
+    __half* O_all = static_cast<__half*>(c->O_all);
+    __half* send_buf = static_cast<__half*>(c->send_buf);
+    __half* output = static_cast<__half*>(dev_out);
+    int* counters = c->counters;
+    const int target = efa_blocks_per_tile(&p);
+    auto ev_in = [&](int i) { return c->events[3 * i]; };
+    auto ev_proj = [&](int i) { return c->events[3 * i + 1]; };
+    auto ev_ar = [&](int i) { return c->events[3 * i + 2]; };
+    cudaEvent_t ev_w = c->events[3 * nchunk], reset_done = c->events[3 * nchunk + 1];
+    const size_t head_pitch = (size_t)p.S * p.d_h * 2;            // bytes between heads, host and device alike
+
+    if (world_barrier(c->world)) return 1;
+    const double t0 = now_ms();
+    EFA_CUDA(cudaMemcpyAsync(dev.W_O, W_O, (size_t)p.d_local * p.d * 2, cudaMemcpyHostToDevice, c->h2d_stream));
+    EFA_CUDA(cudaEventRecord(ev_w, c->h2d_stream));
+    EFA_CUDA(cudaMemsetAsync(counters, 0, (size_t)p.num_tiles * sizeof(int), c->compute_stream));
+    EFA_CUDA(cudaEventRecord(reset_done, c->compute_stream));
+    EFA_CUDA(cudaStreamWaitEvent(c->proj_stream, reset_done, 0));
+    EFA_CUDA(cudaStreamWaitEvent(c->proj_stream, ev_w, 0));
+    for (int i = 0; i < nchunk; i++) {
+        const int t0c = i * ct, nt = (t0c + ct <= p.num_tiles) ? ct : p.num_tiles - t0c;
+        const int row0 = t0c * p.tile, rows = nt * p.tile;
+        const size_t off = (size_t)row0 * p.d_h * 2, width = (size_t)rows * p.d_h * 2;
+        // rows [row0, row0 + rows) of every head: one strided copy per tensor
+        const void* src[3] = {Qh, Kh, Vh};
+        void* dst[3] = {dev.Qh, dev.Kh, dev.Vh};
+        for (int k = 0; k < 3; k++)
+            EFA_CUDA(cudaMemcpy2DAsync(static_cast<char*>(dst[k]) + off, head_pitch, static_cast<const char*>(src[k]) + off, head_pitch,
+                                       width, (size_t)p.H_local, cudaMemcpyHostToDevice, c->h2d_stream));
+        EFA_CUDA(cudaEventRecord(ev_in(i), c->h2d_stream));
+        // causal: rows of chunk i need keys of chunks 0..i only, and those are on the device now
+        EFA_CUDA(cudaStreamWaitEvent(c->compute_stream, ev_in(i), 0));
+        if (r.attention_raw(O_all + (size_t)row0 * p.d_local, rows, row0, rows, c->compute_stream, counters + t0c, p.tile)) return 1;
+        for (int t = t0c; t < t0c + nt; t++)
+            EFA_CU(api->cuStreamWaitValue32((CUstream)c->proj_stream, (CUdeviceptr)(counters + t), (cuuint32_t)target, CU_STREAM_WAIT_VALUE_GEQ));
+        if (r.project(O_all + (size_t)row0 * p.d_local, send_buf + (size_t)row0 * p.d, rows)) return 1;
+        EFA_CUDA(cudaEventRecord(ev_proj(i), c->proj_stream));
+        const int slot = i % c->ncomm;
+        EFA_CUDA(cudaStreamWaitEvent(c->comm_streams[slot], ev_proj(i), 0));
+        if (p.skip_comm) {
+            EFA_CUDA(cudaMemcpyAsync(output + (size_t)row0 * p.d, send_buf + (size_t)row0 * p.d, (size_t)rows * p.d * 2,
+                                     cudaMemcpyDeviceToDevice, c->comm_streams[slot]));
+        } else if (r.allreduce(slot, send_buf + (size_t)row0 * p.d, output + (size_t)row0 * p.d, (size_t)rows * p.d)) return 1;
+        EFA_CUDA(cudaEventRecord(ev_ar(i), c->comm_streams[slot]));
+        if (host_out) {
+            EFA_CUDA(cudaStreamWaitEvent(c->d2h_stream, ev_ar(i), 0));
+            EFA_CUDA(cudaMemcpyAsync(host_out + (size_t)row0 * p.d, output + (size_t)row0 * p.d, (size_t)rows * p.d * 2,
+                                     cudaMemcpyDeviceToHost, c->d2h_stream));
+        }
+    }
+    if (sync_stream(c, c->h2d_stream, nullptr, 0)) return 1;
+    if (sync_stream(c, c->compute_stream, counters, p.num_tiles)) return 1;
+    if (sync_stream(c, c->proj_stream, counters, p.num_tiles)) return 1;
+    if (sync_comm_streams(c)) return 1;
+    if (sync_stream(c, c->d2h_stream, nullptr, 0)) return 1;
+    return finish_timing(c, t0, stats, false, false, r.launches);
+}
+
 int run_mode_impl(efa_ctx* c, int mode, const efa_weights& w, void* output, const efa_params& p, efa_run_stats* stats)
 {
     if (!c) { set_error("run_mode: null context"); return 2; }

@@ -108,6 +108,14 @@ int efa_convert_f32_to_f16(const float* in, void* out, size_t n, void* stream);
 int efa_project_f16(const void* O_tile, const void* W_O, void* out,
                     int rows, int d_local, int d, void* stream);
 
+/* compute_qkv (attn_main.cuh:30-31, attn_main.cu:127-153) on fp16 data, the step before the block:
+ * per local head h, Q_h[S][d_h] = X[S][d] * W_q_h[d][d_h] (and K, V alike) with the projection kernel,
+ * fp32 accumulate, written as fp16 head-major [H_local][S][d_h] directly (the reference computes in
+ * fp32 with cuBLAS and converts in a second pass). X fp16 [S][d]; W_q/W_k/W_v fp16 [H_local][d][d_h].
+ * d_h must be 64 or 128, S a multiple of 64, d a multiple of 16. Untimed in the reference. */
+int efa_compute_qkv_f16(const void* X, const void* W_q, const void* W_k, const void* W_v,
+                        void* Qh, void* Kh, void* Vh, int S, int d, int H_local, int d_h, void* stream);
+
 /* Status word written by kernels whose bounded waits ran out: out4 = {code, block, site, 0};
  * code 0 = no kernel reported a problem since the last efa_kernel_status_reset(). */
 int efa_kernel_status(int* out4);
@@ -209,7 +217,10 @@ int efa_run_mode(efa_ctx* ctx, int mode, const efa_weights* w, void* output,
 
 /* The whole block on HOST buffers: copies this rank's fp16 Q/K/V/W_O to the device, runs `mode`,
  * copies the fp16 [S][d] result back. The copies are inside wall_ms. Buffers should be pinned.
- * Device staging is allocated on the first call for a given shape and reused. */
+ * Device staging is allocated on the first call for a given shape and reused. In stream mode with a
+ * causal mask (and split == 1, NCCL reduction) the work is pipelined over row chunks: rows of chunk c
+ * need only the keys of chunks 0..c, so the copy-in of the next chunk, the attention / projection /
+ * AllReduce of this one and the copy-out of the previous one overlap. */
 int efa_run_mode_host(efa_ctx* ctx, int mode,
                       const uint16_t* Qh, const uint16_t* Kh, const uint16_t* Vh, const uint16_t* W_O,
                       uint16_t* output, const efa_params* p, efa_run_stats* stats);

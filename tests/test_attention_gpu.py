@@ -131,3 +131,28 @@ def test_convert_f32_to_f16(pkg, torch_cuda):
     pkg.convert_f32_to_f16(x, y, x.numel())
     torch.cuda.synchronize()
     assert torch.equal(y, x.to(torch.float16))
+
+
+@pytest.mark.parametrize("S,H_local,d_h,causal", [(16384, 2, 64, 0), (32768, 2, 64, 1), (65536, 2, 64, 1), (65536, 2, 64, 0), (32768, 4, 128, 1)],
+                         ids=lambda v: str(v))
+def test_full_size_rank_shards_on_sampled_rows(pkg, oracle, torch_cuda, S, H_local, d_h, causal):
+    """One rank's shard of the eight-GPU configurations of the benchmark plan (two heads of d_h = 64 at
+    S = 16k/32k/64k; four heads of d_h = 128 at S = 32k), N(0,1) inputs, checked on rows from the first, last
+    and interior tiles, plus a size-independent property: with V = 1 every output element is exactly 1."""
+    torch = torch_cuda
+    R = 8
+    p = pkg.make_params(S, R * H_local * d_h, R * H_local, 128, 2, 1, causal, R)
+    assert p.H_local == H_local
+    bits = [np.zeros((H_local, S, d_h), np.uint16) for _ in range(3)] + [np.zeros((p.d_local, p.d), np.uint16)]
+    pkg.fill_host_inputs(p, 3, 42, pkg.RECIPE_NORMAL, *bits)
+    vals = [oracle.widen_f16(b) for b in bits[:3]]
+    rng = np.random.default_rng(S + d_h)
+    rows = np.unique(np.concatenate([np.arange(0, 24), np.arange(S - 24, S), rng.integers(24, S - 24, 48)])).astype(np.int32)
+    ref = oracle.attention_rows(vals[0], vals[1], vals[2], causal, rows)
+    dev = to_dev(torch, bits[:3])
+    O, counters = run_attention(pkg, torch, p, dev, 0, S, pkg.F16, tile_rows=128)
+    assert counters.cpu().tolist() == [pkg.blocks_per_tile(p)] * (S // 128)
+    assert_close(oracle, O[torch.from_numpy(rows.astype(np.int64)).cuda()].float().cpu().numpy(), ref)
+    ones = torch.ones((H_local, S, d_h), dtype=torch.float16, device="cuda")
+    O1, _ = run_attention(pkg, torch, p, [dev[0], dev[1], ones], 0, S, pkg.F32)
+    assert float((O1 - 1.0).abs().max()) < 2e-3
