@@ -59,7 +59,7 @@ struct WsCfg {
 // with the 1.5*2^23 trick, a degree-3 minimax polynomial for 2^f on [-0.5, 0.5] (relative error 7.5e-5,
 // an order of magnitude below the fp16 rounding P gets anyway), and the integer part added into the
 // exponent field. Only used when EFA_POLY_EVERY > 0.
-__device__ __forceinline__ float ex2_poly(float x)
+__device__ __forceinline__ __attribute__((unused)) float ex2_poly(float x)
 {
     x = fmaxf(x, -126.f);
     const float magic = 12582912.f;                 // 1.5 * 2^23: low mantissa bits of (x + magic) = round(x)
