@@ -19,6 +19,7 @@ struct FaArgs {
     int*    tile_counters;
     int     tile_rows;
     int*    status;
+    int     band_blocks;    // two-tile kernel: 256-row blocks per band of the work order (0 or 1 = strict row order)
 };
 
 __device__ __forceinline__ float ex2(float x)

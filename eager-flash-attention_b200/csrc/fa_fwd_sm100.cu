@@ -432,7 +432,8 @@ const char* fa_check_params(const efa_flash_params& p, int q_rows)
 
 int fa_forward(const void* Q, const void* K, const void* V, void* O, int o_dtype,
                const efa_flash_partials* part, int q_start, int q_rows,
-               const efa_flash_params& p, cudaStream_t stream, int* tile_counters, int tile_rows, int reserve_sms)
+               const efa_flash_params& p, cudaStream_t stream, int* tile_counters, int tile_rows, int reserve_sms,
+               int band_rows)
 {
     if (const char* why = fa_check_params(p, q_rows)) { set_error("flash_attn_tc_forward: %s", why); return 2; }
     if (q_start < 0 || q_start % 64 != 0 || q_start + q_rows > p.S) {
@@ -471,6 +472,7 @@ int fa_forward(const void* Q, const void* K, const void* V, void* O, int o_dtype
     a.scale_log2e = p.scale * 1.4426950408889634f;
     a.tile_counters = tile_counters; a.tile_rows = tile_rows;
     a.status = kernel_status_word();
+    a.band_blocks = (tile_counters == nullptr) ? (q_rows + 255) / 256 : band_rows / 256;
 
     const bool f16 = (o_dtype == EFA_F16);
     // d_h = 64 / 128 run on the warp-specialised two-tile kernel; EFA_ATTN_ONE_TILE=1 (a diagnostics
@@ -604,6 +606,7 @@ int fa_forward_noalloc(const void* Q, const void* K, const void* V, void* O, int
     a.scale_log2e = p.scale * 1.4426950408889634f;
     a.tile_counters = nullptr; a.tile_rows = 0;
     a.status = nullptr;                      // the status word of the other entry points is allocated memory
+    a.band_blocks = 0;
 
     dim3 grid(p.H_local * p.split, (q_rows + FA_BM - 1) / FA_BM);
     const bool f16 = (o_dtype == EFA_F16);

@@ -11,7 +11,10 @@ const char* fa_check_params(const efa_flash_params& p, int q_rows);
 int fa_forward(const void* Q, const void* K, const void* V, void* O, int o_dtype,
                const efa_flash_partials* part, int q_start, int q_rows,
                const efa_flash_params& p, cudaStream_t stream, int* tile_counters, int tile_rows,
-               int reserve_sms = 0);   // > 0 (d_h 64/128 only): persistent grid that leaves that many SMs free
+               int reserve_sms = 0,    // > 0 (d_h 64/128 only): persistent grid that leaves that many SMs free
+               int band_rows = 0);     // d_h 64/128 with counters: rows may complete in bands of this many rows
+                                       // (better K/V reuse in L2); 0 = strict row order. Without counters the
+                                       // order is free and whole heads are processed one after another.
 
 // Split-KV attention + merge with the partials in a fixed device array (no allocation anywhere).
 int fa_forward_noalloc(const void* Q, const void* K, const void* V, void* O, int o_dtype,

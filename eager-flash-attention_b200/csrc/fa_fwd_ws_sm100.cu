@@ -161,7 +161,21 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ,
     const int item = s_item;
     if (item >= items_total || abort_word != 0) return false;
 
-    const int item_x = item % items_x, item_y = item / items_x;
+    // Work order. Strict row order (heads fastest) makes every head's K/V stream live at once, far more than
+    // the L2 holds. With bands, the blocks of one band of rows are taken head by head: the CTAs in flight then
+    // share a few heads' K/V, and rows still complete band by band, which is all a consumer that handles
+    // groups of tiles needs.
+    int item_x, item_y;
+    {
+        const int items_y = items_total / items_x;
+        const int band = a.band_blocks > 1 ? min(a.band_blocks, items_y) : 1;
+        const int per_band = items_x * band;
+        const int full = items_y / band;
+        int b = item / per_band, rem = item - b * per_band, nb = band;
+        if (b >= full) { b = full; rem = item - full * per_band; nb = items_y - full * band; }
+        item_x = rem / nb;
+        item_y = b * band + rem % nb;
+    }
     it.head  = item_x % a.H_local;
     it.split = item_x / a.H_local;
     it.block_row0 = item_y * (2 * WS_BM);
