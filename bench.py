@@ -167,7 +167,8 @@ def main():
                     help="stream mode: per-group NCCL AllReduce, or the persistent projection+reduction kernel over "
                          "peer memory; auto = whichever measured faster for this rank count")
     ap.add_argument("--group-tiles", type=int, default=0, help="tiles per projection + AllReduce launch (0 = auto, 1 = per tile)")
-    ap.add_argument("--cpu-rows", type=int, default=48, help="query rows of the CPU baseline sample (0 = skip)")
+    ap.add_argument("--cpu-rows", type=int, default=2048,
+                    help="query rows of the CPU baseline sample (0 = skip); 2048 rows are about 10 s on 16 host threads")
     ap.add_argument("--S", type=int, default=WORKLOAD["S"], help="override the sequence length (profiling captures only)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.S == WORKLOAD["S"] else args.warmup
