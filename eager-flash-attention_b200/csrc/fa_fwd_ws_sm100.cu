@@ -16,6 +16,13 @@
 // O is rescaled in tensor memory by the softmax warps themselves, and only when a row maximum grew
 // by more than 2^8 since the value last used as the exponent offset (P then stays below 256, well
 // inside fp16); the final division by the row sum makes the result independent of the offset.
+// P reaches the MMA warp in two 64-key halves, each on its own mbarrier, so the first four k-steps of
+// P*V start while the exponentials of the second half are still being computed.
+//
+// Work items (256 rows of one head/split) are taken either one per CTA from the grid, or, in the
+// persistent form, by fewer CTAs than SMs from a global counter; the barriers are rebuilt per item.
+// The order of the items is strict row order, or bands of rows taken head by head when the caller
+// allows rows to complete band by band (see fetch_item).
 //
 // All waits are bounded; a warp leaves its loop as a whole when a wait fails, every other role then
 // runs into its own bounded wait or sees the CTA's abort word, and the CTA frees its tensor memory.
@@ -136,63 +143,63 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ,
     // Next work item. Thread 0 rebuilds the barriers for every item: all threads are past the previous one.
     // Both role branches below call this the same number of times, so its __syncthreads pair up.
     auto fetch_item = [&](int round, ItemInfo& it) -> bool {
-    // ---- next work item; barriers are rebuilt for every item (all threads are past the previous one)
-    if (tid == 0) {
-        s_item = PERSIST ? atomicAdd(work_counter, 1) : (int)(blockIdx.y * gridDim.x + blockIdx.x);
-        half_done[0][0] = half_done[0][1] = half_done[1][0] = half_done[1][1] = 0;
-        if (round > 0) {
-            for (int q = 0; q < 2; q++) { mbar_inval(&q_full[q]); mbar_inval(&s_full[q]); mbar_inval(&p_full[q][0]); mbar_inval(&p_full[q][1]); mbar_inval(&o_done[q]); }
-            for (int s = 0; s < NST; s++) { mbar_inval(&k_full[s]); mbar_inval(&k_empty[s]); mbar_inval(&v_full[s]); mbar_inval(&v_empty[s]); }
+        // ---- next work item; barriers are rebuilt for every item (all threads are past the previous one)
+        if (tid == 0) {
+            s_item = PERSIST ? atomicAdd(work_counter, 1) : (int)(blockIdx.y * gridDim.x + blockIdx.x);
+            half_done[0][0] = half_done[0][1] = half_done[1][0] = half_done[1][1] = 0;
+            if (round > 0) {
+                for (int q = 0; q < 2; q++) { mbar_inval(&q_full[q]); mbar_inval(&s_full[q]); mbar_inval(&p_full[q][0]); mbar_inval(&p_full[q][1]); mbar_inval(&o_done[q]); }
+                for (int s = 0; s < NST; s++) { mbar_inval(&k_full[s]); mbar_inval(&k_empty[s]); mbar_inval(&v_full[s]); mbar_inval(&v_empty[s]); }
+            }
+            for (int q = 0; q < 2; q++) {
+                mbar_init(&q_full[q], 1);
+                mbar_init(&s_full[q], 1);
+                mbar_init(&p_full[q][0], WS_BM);
+                mbar_init(&p_full[q][1], WS_BM);
+                mbar_init(&o_done[q], 1);
+            }
+            for (int s = 0; s < NST; s++) {
+                mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
+                mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
+            }
+            mbar_fence_init();
         }
+        __syncthreads();
+        const int item = s_item;
+        if (item >= items_total || abort_word != 0) return false;
+
+        // Work order. Strict row order (heads fastest) makes every head's K/V stream live at once, far more than
+        // the L2 holds. With bands, the blocks of one band of rows are taken head by head: the CTAs in flight then
+        // share a few heads' K/V, and rows still complete band by band, which is all a consumer that handles
+        // groups of tiles needs.
+        int item_x, item_y;
+        {
+            const int items_y = items_total / items_x;
+            const int band = a.band_blocks > 1 ? min(a.band_blocks, items_y) : 1;
+            const int per_band = items_x * band;
+            const int full = items_y / band;
+            int b = item / per_band, rem = item - b * per_band, nb = band;
+            if (b >= full) { b = full; rem = item - full * per_band; nb = items_y - full * band; }
+            item_x = rem / nb;
+            item_y = b * band + rem % nb;
+        }
+        it.head  = item_x % a.H_local;
+        it.split = item_x / a.H_local;
+        it.block_row0 = item_y * (2 * WS_BM);
+        const int rows_valid = min(2 * WS_BM, a.q_rows - it.block_row0);      // 64, 128, 192 or 256
+        it.kv_lo = it.split * kv_len;
+        it.kv_hi = it.kv_lo + kv_len;
+
+        // Per Q tile: first absolute row, valid rows, number of key stages.
+        #pragma unroll
         for (int q = 0; q < 2; q++) {
-            mbar_init(&q_full[q], 1);
-            mbar_init(&s_full[q], 1);
-            mbar_init(&p_full[q][0], WS_BM);
-            mbar_init(&p_full[q][1], WS_BM);
-            mbar_init(&o_done[q], 1);
+            it.q_abs0[q] = a.q_start + it.block_row0 + q * WS_BM;
+            it.rows_q[q] = max(0, min(WS_BM, rows_valid - q * WS_BM));
+            const int kv_end = a.causal ? min(it.kv_hi, it.q_abs0[q] + it.rows_q[q]) : it.kv_hi;
+            it.nblk[q] = (it.rows_q[q] > 0 && kv_end > it.kv_lo) ? (kv_end - it.kv_lo + WS_BN - 1) / WS_BN : 0;
         }
-        for (int s = 0; s < NST; s++) {
-            mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
-            mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
-        }
-        mbar_fence_init();
-    }
-    __syncthreads();
-    const int item = s_item;
-    if (item >= items_total || abort_word != 0) return false;
-
-    // Work order. Strict row order (heads fastest) makes every head's K/V stream live at once, far more than
-    // the L2 holds. With bands, the blocks of one band of rows are taken head by head: the CTAs in flight then
-    // share a few heads' K/V, and rows still complete band by band, which is all a consumer that handles
-    // groups of tiles needs.
-    int item_x, item_y;
-    {
-        const int items_y = items_total / items_x;
-        const int band = a.band_blocks > 1 ? min(a.band_blocks, items_y) : 1;
-        const int per_band = items_x * band;
-        const int full = items_y / band;
-        int b = item / per_band, rem = item - b * per_band, nb = band;
-        if (b >= full) { b = full; rem = item - full * per_band; nb = items_y - full * band; }
-        item_x = rem / nb;
-        item_y = b * band + rem % nb;
-    }
-    it.head  = item_x % a.H_local;
-    it.split = item_x / a.H_local;
-    it.block_row0 = item_y * (2 * WS_BM);
-    const int rows_valid = min(2 * WS_BM, a.q_rows - it.block_row0);      // 64, 128, 192 or 256
-    it.kv_lo = it.split * kv_len;
-    it.kv_hi = it.kv_lo + kv_len;
-
-    // Per Q tile: first absolute row, valid rows, number of key stages.
-    #pragma unroll
-    for (int q = 0; q < 2; q++) {
-        it.q_abs0[q] = a.q_start + it.block_row0 + q * WS_BM;
-        it.rows_q[q] = max(0, min(WS_BM, rows_valid - q * WS_BM));
-        const int kv_end = a.causal ? min(it.kv_hi, it.q_abs0[q] + it.rows_q[q]) : it.kv_hi;
-        it.nblk[q] = (it.rows_q[q] > 0 && kv_end > it.kv_lo) ? (kv_end - it.kv_lo + WS_BN - 1) / WS_BN : 0;
-    }
-    it.nblk_max = max(it.nblk[0], it.nblk[1]);
-    return true;
+        it.nblk_max = max(it.nblk[0], it.nblk[1]);
+        return true;
     };
     auto end_item = [&]() {
         __syncwarp();
@@ -208,283 +215,283 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ,
     if (warp >= 8) {
         setmaxnreg_dec_56();
         for (int round = 0; ; round++) {
-        ItemInfo it;
-        if (!fetch_item(round, it)) break;
-        EFA_ITEM_LOCALS
-        // =====================================================================================
-        // Producer / MMA warpgroup
-        // =====================================================================================
-        if (warp == 8 && lane == 0) {
-            // ---- TMA producer
-            auto load_tile = [&](uint8_t* dst, const CUtensorMap* tm, uint64_t* bar, int row) {
-                mbar_expect_tx(bar, C::TILE_BYTES);
-                #pragma unroll
-                for (int b = 0; b < C::NBOX; b++)
-                    tma_load_3d(dst + b * C::BOX_BYTES, tm, bar, b * C::BOXC, row, head);
-            };
-            for (int q = 0; q < 2; q++)
-                if (nblk[q] > 0) load_tile(sQ + q * C::TILE_BYTES, &tmQ, &q_full[q], q_abs0[q]);
-            for (int j = 0; j < nblk_max; j++) {
-                const int s = j % NST, u = j / NST;
-                if (u > 0 && !mbar_wait(&k_empty[s], (uint32_t)((u - 1) & 1), &abort_word, 21)) break;
-                load_tile(sK + s * C::TILE_BYTES, &tmK, &k_full[s], kv_lo + j * WS_BN);
-                if (u > 0 && !mbar_wait(&v_empty[s], (uint32_t)((u - 1) & 1), &abort_word, 22)) break;
-                load_tile(sV + s * C::TILE_BYTES, &tmV, &v_full[s], kv_lo + j * WS_BN);
-            }
-        } else if (warp == 9 && lane == 0) {
-            // ---- MMA issuer
-            auto issue_qk = [&](int q, int stage) {
-                const uint32_t qa = smem_u32(sQ + q * C::TILE_BYTES);
-                const uint32_t ka = smem_u32(sK + stage * C::TILE_BYTES);
-                #pragma unroll
-                for (int ks = 0; ks < D / 16; ks++) {
-                    const uint32_t off = (uint32_t)((ks * 16) / C::BOXC) * C::BOX_BYTES + (uint32_t)((ks * 16) % C::BOXC) * 2u;
-                    tc_mma_ss(tmem_base + q * 128, smem_desc(qa + off, 16, 1024, SWZ), smem_desc(ka + off, 16, 1024, SWZ),
-                              IDESC_QK, ks > 0 ? 1u : 0u);
+            ItemInfo it;
+            if (!fetch_item(round, it)) break;
+            EFA_ITEM_LOCALS
+            // =====================================================================================
+            // Producer / MMA warpgroup
+            // =====================================================================================
+            if (warp == 8 && lane == 0) {
+                // ---- TMA producer
+                auto load_tile = [&](uint8_t* dst, const CUtensorMap* tm, uint64_t* bar, int row) {
+                    mbar_expect_tx(bar, C::TILE_BYTES);
+                    #pragma unroll
+                    for (int b = 0; b < C::NBOX; b++)
+                        tma_load_3d(dst + b * C::BOX_BYTES, tm, bar, b * C::BOXC, row, head);
+                };
+                for (int q = 0; q < 2; q++)
+                    if (nblk[q] > 0) load_tile(sQ + q * C::TILE_BYTES, &tmQ, &q_full[q], q_abs0[q]);
+                for (int j = 0; j < nblk_max; j++) {
+                    const int s = j % NST, u = j / NST;
+                    if (u > 0 && !mbar_wait(&k_empty[s], (uint32_t)((u - 1) & 1), &abort_word, 21)) break;
+                    load_tile(sK + s * C::TILE_BYTES, &tmK, &k_full[s], kv_lo + j * WS_BN);
+                    if (u > 0 && !mbar_wait(&v_empty[s], (uint32_t)((u - 1) & 1), &abort_word, 22)) break;
+                    load_tile(sV + s * C::TILE_BYTES, &tmV, &v_full[s], kv_lo + j * WS_BN);
                 }
-            };
-            auto issue_pv = [&](int q, int stage, bool first, int half) {
-                const uint32_t va = smem_u32(sV + stage * C::TILE_BYTES);
-                #pragma unroll
-                for (int ks = half * 4; ks < half * 4 + 4; ks++)
-                    tc_mma_ts(tmem_base + 256 + q * 128, tmem_base + q * 128 + ks * 8,
-                              smem_desc(va + ks * 16 * 128, C::BOX_BYTES, 1024, SWZ), IDESC_PV, (!first || ks > 0) ? 1u : 0u);
-            };
-            bool ok = true;
-            if (nblk_max > 0) {
-                ok = mbar_wait(&k_full[0], 0, &abort_word, 23);
-                for (int q = 0; q < 2 && ok; q++) {
-                    if (nblk[q] > 0) {
-                        ok = mbar_wait(&q_full[q], 0, &abort_word, 24);
-                        if (!ok) break;
-                        tc_fence_after_sync();
-                        issue_qk(q, 0);
-                        tc_commit(&s_full[q]);
+            } else if (warp == 9 && lane == 0) {
+                // ---- MMA issuer
+                auto issue_qk = [&](int q, int stage) {
+                    const uint32_t qa = smem_u32(sQ + q * C::TILE_BYTES);
+                    const uint32_t ka = smem_u32(sK + stage * C::TILE_BYTES);
+                    #pragma unroll
+                    for (int ks = 0; ks < D / 16; ks++) {
+                        const uint32_t off = (uint32_t)((ks * 16) / C::BOXC) * C::BOX_BYTES + (uint32_t)((ks * 16) % C::BOXC) * 2u;
+                        tc_mma_ss(tmem_base + q * 128, smem_desc(qa + off, 16, 1024, SWZ), smem_desc(ka + off, 16, 1024, SWZ),
+                                  IDESC_QK, ks > 0 ? 1u : 0u);
                     }
-                }
-                if (ok) tc_commit(&k_empty[0]);
-            }
-            for (int j = 0; j < nblk_max && ok; j++) {
-                const int s = j % NST;
-                ok = mbar_wait(&v_full[s], (uint32_t)((j / NST) & 1), &abort_word, 25);
-                if (!ok) break;
-                bool k_next_ready = false;
-                for (int q = 0; q < 2 && ok; q++) {
-                    if (j >= nblk[q]) continue;
-                    ok = mbar_wait(&p_full[q][0], (uint32_t)(j & 1), &abort_word, 26);
-                    if (!ok) break;
-                    tc_fence_after_sync();
-                    issue_pv(q, s, j == 0, 0);
-                    ok = mbar_wait(&p_full[q][1], (uint32_t)(j & 1), &abort_word, 29);
-                    if (!ok) break;
-                    tc_fence_after_sync();
-                    issue_pv(q, s, j == 0, 1);
-                    if (j + 1 < nblk[q]) {
-                        const int ns = (j + 1) % NST;
-                        if (!k_next_ready) {
-                            ok = mbar_wait(&k_full[ns], (uint32_t)(((j + 1) / NST) & 1), &abort_word, 27);
+                };
+                auto issue_pv = [&](int q, int stage, bool first, int half) {
+                    const uint32_t va = smem_u32(sV + stage * C::TILE_BYTES);
+                    #pragma unroll
+                    for (int ks = half * 4; ks < half * 4 + 4; ks++)
+                        tc_mma_ts(tmem_base + 256 + q * 128, tmem_base + q * 128 + ks * 8,
+                                  smem_desc(va + ks * 16 * 128, C::BOX_BYTES, 1024, SWZ), IDESC_PV, (!first || ks > 0) ? 1u : 0u);
+                };
+                bool ok = true;
+                if (nblk_max > 0) {
+                    ok = mbar_wait(&k_full[0], 0, &abort_word, 23);
+                    for (int q = 0; q < 2 && ok; q++) {
+                        if (nblk[q] > 0) {
+                            ok = mbar_wait(&q_full[q], 0, &abort_word, 24);
                             if (!ok) break;
                             tc_fence_after_sync();
-                            k_next_ready = true;
+                            issue_qk(q, 0);
+                            tc_commit(&s_full[q]);
                         }
-                        issue_qk(q, ns);
-                        tc_commit(&s_full[q]);
-                    } else {
-                        tc_commit(&o_done[q]);
                     }
+                    if (ok) tc_commit(&k_empty[0]);
                 }
-                if (!ok) break;
-                tc_commit(&v_empty[s]);
-                if (j + 1 < nblk_max) tc_commit(&k_empty[(j + 1) % NST]);
+                for (int j = 0; j < nblk_max && ok; j++) {
+                    const int s = j % NST;
+                    ok = mbar_wait(&v_full[s], (uint32_t)((j / NST) & 1), &abort_word, 25);
+                    if (!ok) break;
+                    bool k_next_ready = false;
+                    for (int q = 0; q < 2 && ok; q++) {
+                        if (j >= nblk[q]) continue;
+                        ok = mbar_wait(&p_full[q][0], (uint32_t)(j & 1), &abort_word, 26);
+                        if (!ok) break;
+                        tc_fence_after_sync();
+                        issue_pv(q, s, j == 0, 0);
+                        ok = mbar_wait(&p_full[q][1], (uint32_t)(j & 1), &abort_word, 29);
+                        if (!ok) break;
+                        tc_fence_after_sync();
+                        issue_pv(q, s, j == 0, 1);
+                        if (j + 1 < nblk[q]) {
+                            const int ns = (j + 1) % NST;
+                            if (!k_next_ready) {
+                                ok = mbar_wait(&k_full[ns], (uint32_t)(((j + 1) / NST) & 1), &abort_word, 27);
+                                if (!ok) break;
+                                tc_fence_after_sync();
+                                k_next_ready = true;
+                            }
+                            issue_qk(q, ns);
+                            tc_commit(&s_full[q]);
+                        } else {
+                            tc_commit(&o_done[q]);
+                        }
+                    }
+                    if (!ok) break;
+                    tc_commit(&v_empty[s]);
+                    if (j + 1 < nblk_max) tc_commit(&k_empty[(j + 1) % NST]);
+                }
+                // The last commit has to land before the barriers are rebuilt for the next work item.
+                if (ok && nblk_max > 0)
+                    mbar_wait(&v_empty[(nblk_max - 1) % NST], (uint32_t)(((nblk_max - 1) / NST) & 1), &abort_word, 28);
             }
-            // The last commit has to land before the barriers are rebuilt for the next work item.
-            if (ok && nblk_max > 0)
-                mbar_wait(&v_empty[(nblk_max - 1) % NST], (uint32_t)(((nblk_max - 1) / NST) & 1), &abort_word, 28);
-        }
-        end_item();
-        if (!PERSIST) break;
+            end_item();
+            if (!PERSIST) break;
         }
     } else {
         setmaxnreg_inc_224();
         for (int round = 0; ; round++) {
-        ItemInfo it;
-        if (!fetch_item(round, it)) break;
-        EFA_ITEM_LOCALS
-        // =====================================================================================
-        // Softmax warpgroups: tile q = warp / 4, row = thread index within the warpgroup
-        // =====================================================================================
-        const int q = warp >> 2;
-        const int row = tid - q * WS_BM;
-        const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-        const uint32_t tmem_S = tmem_base + q * 128 + lane_base;
-        const uint32_t tmem_O = tmem_base + 256 + q * 128 + lane_base;
-        const int my_rows = rows_q[q];
-        const int my_nblk = nblk[q];
-        const int my_abs0 = q_abs0[q];
+            ItemInfo it;
+            if (!fetch_item(round, it)) break;
+            EFA_ITEM_LOCALS
+            // =====================================================================================
+            // Softmax warpgroups: tile q = warp / 4, row = thread index within the warpgroup
+            // =====================================================================================
+            const int q = warp >> 2;
+            const int row = tid - q * WS_BM;
+            const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+            const uint32_t tmem_S = tmem_base + q * 128 + lane_base;
+            const uint32_t tmem_O = tmem_base + 256 + q * 128 + lane_base;
+            const int my_rows = rows_q[q];
+            const int my_nblk = nblk[q];
+            const int my_abs0 = q_abs0[q];
 
-        float m_ref = kNegInfW;     // exponent offset in use (a past row maximum), scaled by scale*log2(e)
-        float m_true = kNegInfW;    // true running row maximum, same scaling
-        float l_run = 0.f;          // running denominator relative to m_ref
-        bool ok = true;
+            float m_ref = kNegInfW;     // exponent offset in use (a past row maximum), scaled by scale*log2(e)
+            float m_true = kNegInfW;    // true running row maximum, same scaling
+            float l_run = 0.f;          // running denominator relative to m_ref
+            bool ok = true;
 
-        for (int j = 0; j < my_nblk; j++) {
-            const int kb = kv_lo + j * WS_BN;
-            ok = __all_sync(0xffffffffu, mbar_wait(&s_full[q], (uint32_t)(j & 1), &abort_word, 31));
-            if (!ok) break;
-            tc_fence_after_sync();
+            for (int j = 0; j < my_nblk; j++) {
+                const int kb = kv_lo + j * WS_BN;
+                ok = __all_sync(0xffffffffu, mbar_wait(&s_full[q], (uint32_t)(j & 1), &abort_word, 31));
+                if (!ok) break;
+                tc_fence_after_sync();
 
-            uint32_t su[4][32];
-            #pragma unroll
-            for (int c = 0; c < 4; c++) tmem_ld32(tmem_S + c * 32, su[c]);
-            tmem_wait_ld();
-
-            const bool need_mask = (kb + WS_BN > kv_hi) || (a.causal && kb + WS_BN - 1 > my_abs0);
-            if (need_mask) {
-                int lim = kv_hi - 1 - kb;
-                if (a.causal) lim = min(lim, my_abs0 + row - kb);
+                uint32_t su[4][32];
                 #pragma unroll
-                for (int c = 0; c < 4; c++)
+                for (int c = 0; c < 4; c++) tmem_ld32(tmem_S + c * 32, su[c]);
+                tmem_wait_ld();
+
+                const bool need_mask = (kb + WS_BN > kv_hi) || (a.causal && kb + WS_BN - 1 > my_abs0);
+                if (need_mask) {
+                    int lim = kv_hi - 1 - kb;
+                    if (a.causal) lim = min(lim, my_abs0 + row - kb);
                     #pragma unroll
-                    for (int i = 0; i < 32; i++)
-                        if (c * 32 + i > lim) su[c][i] = 0xff800000u;
-            }
+                    for (int c = 0; c < 4; c++)
+                        #pragma unroll
+                        for (int i = 0; i < 32; i++)
+                            if (c * 32 + i > lim) su[c][i] = 0xff800000u;
+                }
 
-            // row maximum: four independent chains of three-input max (half the instructions of fmaxf)
-            float mx0 = kNegInfW, mx1 = kNegInfW, mx2 = kNegInfW, mx3 = kNegInfW;
-            #pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-                mx0 = max3(mx0, __uint_as_float(su[0][i]), __uint_as_float(su[0][i + 1]));
-                mx1 = max3(mx1, __uint_as_float(su[1][i]), __uint_as_float(su[1][i + 1]));
-                mx2 = max3(mx2, __uint_as_float(su[2][i]), __uint_as_float(su[2][i + 1]));
-                mx3 = max3(mx3, __uint_as_float(su[3][i]), __uint_as_float(su[3][i + 1]));
-            }
-            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-            m_true = fmaxf(m_true, mx * a.scale_log2e);
-
-            // Move the exponent offset only when the maximum grew by more than the threshold.
-            float alpha = 1.f;
-            if (m_true - m_ref > kRescaleThreshold || m_ref == kNegInfW) {     // (-inf) - (-inf) is NaN: second test
-                const float m_new = m_true;
-                const float m_use = (m_new == kNegInfW) ? 0.f : m_new;
-                alpha = (m_ref == kNegInfW) ? 0.f : ex2(m_ref - m_use);
-                m_ref = m_new;
-            }
-            const float m_off = (m_ref == kNegInfW) ? 0.f : m_ref;
-
-            // S(j) complete implies PV(j-1) of this tile complete (the tensor pipe runs in order), and no
-            // part of PV(j) is issued before this thread's first arrival below: O may be rescaled here.
-            if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+                // row maximum: four independent chains of three-input max (half the instructions of fmaxf)
+                float mx0 = kNegInfW, mx1 = kNegInfW, mx2 = kNegInfW, mx3 = kNegInfW;
                 #pragma unroll
-                for (int c = 0; c < D / 32; c++) {
-                    uint32_t o[32];
-                    tmem_ld32(tmem_O + c * 32, o);
-                    tmem_wait_ld();
+                for (int i = 0; i < 32; i += 2) {
+                    mx0 = max3(mx0, __uint_as_float(su[0][i]), __uint_as_float(su[0][i + 1]));
+                    mx1 = max3(mx1, __uint_as_float(su[1][i]), __uint_as_float(su[1][i + 1]));
+                    mx2 = max3(mx2, __uint_as_float(su[2][i]), __uint_as_float(su[2][i + 1]));
+                    mx3 = max3(mx3, __uint_as_float(su[3][i]), __uint_as_float(su[3][i + 1]));
+                }
+                const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+                m_true = fmaxf(m_true, mx * a.scale_log2e);
+
+                // Move the exponent offset only when the maximum grew by more than the threshold.
+                float alpha = 1.f;
+                if (m_true - m_ref > kRescaleThreshold || m_ref == kNegInfW) {     // (-inf) - (-inf) is NaN: second test
+                    const float m_new = m_true;
+                    const float m_use = (m_new == kNegInfW) ? 0.f : m_new;
+                    alpha = (m_ref == kNegInfW) ? 0.f : ex2(m_ref - m_use);
+                    m_ref = m_new;
+                }
+                const float m_off = (m_ref == kNegInfW) ? 0.f : m_ref;
+
+                // S(j) complete implies PV(j-1) of this tile complete (the tensor pipe runs in order), and no
+                // part of PV(j) is issued before this thread's first arrival below: O may be rescaled here.
+                if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
                     #pragma unroll
-                    for (int i = 0; i < 32; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                    tmem_st32(tmem_O + c * 32, o);
+                    for (int c = 0; c < D / 32; c++) {
+                        uint32_t o[32];
+                        tmem_ld32(tmem_O + c * 32, o);
+                        tmem_wait_ld();
+                        #pragma unroll
+                        for (int i = 0; i < 32; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tmem_st32(tmem_O + c * 32, o);
+                    }
                 }
-            }
 
-            // P is handed to the MMA warp in two halves of 64 keys: the first four k-steps of P*V run on
-            // the tensor pipe while the exponentials of the second half are still being computed.
-            float ps0 = 0.f, ps1 = 0.f;
-            #pragma unroll
-            for (int c = 0; c < 4; c++) {
-                uint32_t pk[16];
+                // P is handed to the MMA warp in two halves of 64 keys: the first four k-steps of P*V run on
+                // the tensor pipe while the exponentials of the second half are still being computed.
+                float ps0 = 0.f, ps1 = 0.f;
                 #pragma unroll
-                for (int i = 0; i < 16; i++) {
-                    const float x0 = fmaf(__uint_as_float(su[c][2 * i]),     a.scale_log2e, -m_off);
-                    const float x1 = fmaf(__uint_as_float(su[c][2 * i + 1]), a.scale_log2e, -m_off);
-                    const float p0 = ex2(x0);
-                    float p1;
-                    if constexpr (kPolyEvery > 0) p1 = (((2 * i + 1) % (kPolyEvery > 0 ? kPolyEvery : 1)) == kPolyEvery - 1) ? ex2_poly(x1) : ex2(x1);
-                    else p1 = ex2(x1);
-                    ps0 += p0;
-                    ps1 += p1;
-                    pk[i] = pack_f16x2(p0, p1);
+                for (int c = 0; c < 4; c++) {
+                    uint32_t pk[16];
+                    #pragma unroll
+                    for (int i = 0; i < 16; i++) {
+                        const float x0 = fmaf(__uint_as_float(su[c][2 * i]),     a.scale_log2e, -m_off);
+                        const float x1 = fmaf(__uint_as_float(su[c][2 * i + 1]), a.scale_log2e, -m_off);
+                        const float p0 = ex2(x0);
+                        float p1;
+                        if constexpr (kPolyEvery > 0) p1 = (((2 * i + 1) % (kPolyEvery > 0 ? kPolyEvery : 1)) == kPolyEvery - 1) ? ex2_poly(x1) : ex2(x1);
+                        else p1 = ex2(x1);
+                        ps0 += p0;
+                        ps1 += p1;
+                        pk[i] = pack_f16x2(p0, p1);
+                    }
+                    tmem_st16(tmem_S + c * 16, pk);
+                    if (c == 1 || c == 3) {
+                        tmem_wait_st();
+                        tc_fence_before_sync();
+                        mbar_arrive(&p_full[q][c >> 1]);
+                    }
                 }
-                tmem_st16(tmem_S + c * 16, pk);
-                if (c == 1 || c == 3) {
-                    tmem_wait_st();
-                    tc_fence_before_sync();
-                    mbar_arrive(&p_full[q][c >> 1]);
-                }
+                l_run = l_run * alpha + (ps0 + ps1);
             }
-            l_run = l_run * alpha + (ps0 + ps1);
-        }
 
-        if (ok && my_nblk > 0) {
-            ok = __all_sync(0xffffffffu, mbar_wait(&o_done[q], 0, &abort_word, 32));
-            tc_fence_after_sync();
-        }
-
-        // ---- epilogue: this thread's row (warps take this branch as a whole: my_rows is 0, 64 or 128)
-        if (ok && (warp & 3) * 32 < my_rows) {
-            const size_t ld_o = (size_t)a.H_local * D;
-            const size_t orow = (size_t)block_row0 + q * WS_BM + row;
-            float mult;
-            float*  dst32 = nullptr;
-            __half* dst16 = nullptr;
-            if (a.nsplit == 1) {
-                mult = 1.f / l_run;
-                if constexpr (OUT_F16) dst16 = a.O16 + orow * ld_o + (size_t)head * D;
-                else                   dst32 = a.O32 + orow * ld_o + (size_t)head * D;
-            } else {
-                // partials are stored relative to the true row maximum
-                mult = (m_true == kNegInfW) ? 0.f : ex2(m_ref - m_true);
-                dst32 = a.O_part + ((size_t)split * a.part_rows + orow) * ld_o + (size_t)head * D;
-                const size_t s0 = ((size_t)split * a.part_rows + orow) * a.H_local + head;
-                a.m_part[s0] = m_true;
-                a.l_part[s0] = l_run * mult;
+            if (ok && my_nblk > 0) {
+                ok = __all_sync(0xffffffffu, mbar_wait(&o_done[q], 0, &abort_word, 32));
+                tc_fence_after_sync();
             }
-            #pragma unroll
-            for (int c = 0; c < D / 16; c++) {
-                uint32_t o[16];
-                if (my_nblk > 0) {
-                    tmem_ld16(tmem_O + c * 16, o);
-                    tmem_wait_ld();
+
+            // ---- epilogue: this thread's row (warps take this branch as a whole: my_rows is 0, 64 or 128)
+            if (ok && (warp & 3) * 32 < my_rows) {
+                const size_t ld_o = (size_t)a.H_local * D;
+                const size_t orow = (size_t)block_row0 + q * WS_BM + row;
+                float mult;
+                float*  dst32 = nullptr;
+                __half* dst16 = nullptr;
+                if (a.nsplit == 1) {
+                    mult = 1.f / l_run;
+                    if constexpr (OUT_F16) dst16 = a.O16 + orow * ld_o + (size_t)head * D;
+                    else                   dst32 = a.O32 + orow * ld_o + (size_t)head * D;
                 } else {
-                    #pragma unroll
-                    for (int i = 0; i < 16; i++) o[i] = 0u;
+                    // partials are stored relative to the true row maximum
+                    mult = (m_true == kNegInfW) ? 0.f : ex2(m_ref - m_true);
+                    dst32 = a.O_part + ((size_t)split * a.part_rows + orow) * ld_o + (size_t)head * D;
+                    const size_t s0 = ((size_t)split * a.part_rows + orow) * a.H_local + head;
+                    a.m_part[s0] = m_true;
+                    a.l_part[s0] = l_run * mult;
                 }
-                if (dst16) {
-                    uint4 v0, v1;
-                    v0.x = pack_f16x2(__uint_as_float(o[0]) * mult,  __uint_as_float(o[1]) * mult);
-                    v0.y = pack_f16x2(__uint_as_float(o[2]) * mult,  __uint_as_float(o[3]) * mult);
-                    v0.z = pack_f16x2(__uint_as_float(o[4]) * mult,  __uint_as_float(o[5]) * mult);
-                    v0.w = pack_f16x2(__uint_as_float(o[6]) * mult,  __uint_as_float(o[7]) * mult);
-                    v1.x = pack_f16x2(__uint_as_float(o[8]) * mult,  __uint_as_float(o[9]) * mult);
-                    v1.y = pack_f16x2(__uint_as_float(o[10]) * mult, __uint_as_float(o[11]) * mult);
-                    v1.z = pack_f16x2(__uint_as_float(o[12]) * mult, __uint_as_float(o[13]) * mult);
-                    v1.w = pack_f16x2(__uint_as_float(o[14]) * mult, __uint_as_float(o[15]) * mult);
-                    uint4* d = reinterpret_cast<uint4*>(dst16 + c * 16);
-                    d[0] = v0;
-                    d[1] = v1;
-                } else {
-                    float4* d = reinterpret_cast<float4*>(dst32 + c * 16);
-                    #pragma unroll
-                    for (int qd = 0; qd < 4; qd++)
-                        d[qd] = make_float4(__uint_as_float(o[4 * qd]) * mult, __uint_as_float(o[4 * qd + 1]) * mult,
-                                            __uint_as_float(o[4 * qd + 2]) * mult, __uint_as_float(o[4 * qd + 3]) * mult);
+                #pragma unroll
+                for (int c = 0; c < D / 16; c++) {
+                    uint32_t o[16];
+                    if (my_nblk > 0) {
+                        tmem_ld16(tmem_O + c * 16, o);
+                        tmem_wait_ld();
+                    } else {
+                        #pragma unroll
+                        for (int i = 0; i < 16; i++) o[i] = 0u;
+                    }
+                    if (dst16) {
+                        uint4 v0, v1;
+                        v0.x = pack_f16x2(__uint_as_float(o[0]) * mult,  __uint_as_float(o[1]) * mult);
+                        v0.y = pack_f16x2(__uint_as_float(o[2]) * mult,  __uint_as_float(o[3]) * mult);
+                        v0.z = pack_f16x2(__uint_as_float(o[4]) * mult,  __uint_as_float(o[5]) * mult);
+                        v0.w = pack_f16x2(__uint_as_float(o[6]) * mult,  __uint_as_float(o[7]) * mult);
+                        v1.x = pack_f16x2(__uint_as_float(o[8]) * mult,  __uint_as_float(o[9]) * mult);
+                        v1.y = pack_f16x2(__uint_as_float(o[10]) * mult, __uint_as_float(o[11]) * mult);
+                        v1.z = pack_f16x2(__uint_as_float(o[12]) * mult, __uint_as_float(o[13]) * mult);
+                        v1.w = pack_f16x2(__uint_as_float(o[14]) * mult, __uint_as_float(o[15]) * mult);
+                        uint4* d = reinterpret_cast<uint4*>(dst16 + c * 16);
+                        d[0] = v0;
+                        d[1] = v1;
+                    } else {
+                        float4* d = reinterpret_cast<float4*>(dst32 + c * 16);
+                        #pragma unroll
+                        for (int qd = 0; qd < 4; qd++)
+                            d[qd] = make_float4(__uint_as_float(o[4 * qd]) * mult, __uint_as_float(o[4 * qd + 1]) * mult,
+                                                __uint_as_float(o[4 * qd + 2]) * mult, __uint_as_float(o[4 * qd + 3]) * mult);
+                    }
                 }
-            }
 
-            // ---- completion signal: one count per finished 64-row block, after its rows are visible.
-            // A 64-row block is two warps; the second of them to get here publishes the count.
-            if (a.tile_counters != nullptr) {
-                __threadfence();
-                __syncwarp();
-                if (lane == 0) {
-                    const int half = (warp & 3) >> 1;
-                    if (atomicAdd(&half_done[q][half], 1) == 1) {
-                        __threadfence();
-                        atomicAdd(a.tile_counters + (block_row0 + q * WS_BM + half * 64) / a.tile_rows, 1);
+                // ---- completion signal: one count per finished 64-row block, after its rows are visible.
+                // A 64-row block is two warps; the second of them to get here publishes the count.
+                if (a.tile_counters != nullptr) {
+                    __threadfence();
+                    __syncwarp();
+                    if (lane == 0) {
+                        const int half = (warp & 3) >> 1;
+                        if (atomicAdd(&half_done[q][half], 1) == 1) {
+                            __threadfence();
+                            atomicAdd(a.tile_counters + (block_row0 + q * WS_BM + half * 64) / a.tile_rows, 1);
+                        }
                     }
                 }
             }
-        }
-        end_item();
-        if (!PERSIST) break;
+            end_item();
+            if (!PERSIST) break;
         }
     }
 #undef EFA_ITEM_LOCALS
