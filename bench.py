@@ -322,7 +322,12 @@ def main():
             roofline=dict(bound="tensor", kernel="fa_fwd_ws_kernel<128>", achieved=achieved, peak=pk["tflops"], unit="TFLOP/s",
                           frac=achieved / pk["tflops"], peak_source=f"of {pk['source']} (burst bf16)",
                           frac_sustained=achieved / pk["tflops_sustained"], attn_kernel_ms=attn_ms,
-                          algorithmic_flops=fl, traffic=None),
+                          algorithmic_flops=fl,
+                          # dram__bytes_read+write of this kernel in stream mode, captured at S=8192 (0.834 GB per
+                          # launch, profiles/fa_fwd_ws_kernel_d128_S8192.md) and scaled by algorithmic FLOPs: an
+                          # estimate, the full-size launch is too long for a multi-pass capture
+                          traffic=(0.834e9 * fl / attention_flops(8192, 128, 32, 1)) if (p.causal and p.d_h == 128) else None,
+                          traffic_note="scaled from an ncu capture at S=8192 by algorithmic FLOPs (estimate)"),
             cpu_baseline=cpu,
             e2e=dict(value=e2e_ms, unit="ms", h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h),
             gpu_launches=launches * args.steps,
