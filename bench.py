@@ -167,6 +167,8 @@ def main():
                     help="stream mode: per-group NCCL AllReduce, or the persistent projection+reduction kernel over "
                          "peer memory; auto = whichever measured faster for this rank count")
     ap.add_argument("--group-tiles", type=int, default=0, help="tiles per projection + AllReduce launch (0 = auto, 1 = per tile)")
+    ap.add_argument("--split", type=int, default=0,
+                    help="split-KV factor of the attention kernel (the reference's --split); 0 = the value chosen for this rank count")
     ap.add_argument("--cpu-rows", type=int, default=2048,
                     help="query rows of the CPU baseline sample (0 = skip); 2048 rows are about 10 s on 16 host threads")
     ap.add_argument("--S", type=int, default=WORKLOAD["S"], help="override the sequence length (profiling captures only)")
@@ -202,6 +204,8 @@ def main():
     W = dict(WORKLOAD)
     W["S"] = args.S
     d = W["H"] * W["d_h"]
+    if args.split > 0:
+        W["split"] = args.split
     p = pkg.make_params(W["S"], d, W["H"], W["tile"], W["nbuf"], W["split"], W["causal"], world_size)
     why = pkg.attn_check_params(p)
     if why:
@@ -311,7 +315,7 @@ def main():
             ms_per_step=ms, higher_is_better=False, scaling="strong", vs_baseline=None, dtype="f16 (f32 accumulate)",
             data="synthetic",
             config=dict(workload=f"S={p.S} H={p.H} d_h={p.d_h} causal tile={p.tile} ncomm={W['ncomm']} TP={world_size}",
-                        mode=args.mode, reduce=args.reduce, group_tiles=args.group_tiles or "auto (S/8 rows per launch)",
+                        mode=args.mode, split=p.split, reduce=args.reduce, group_tiles=args.group_tiles or "auto (S/8 rows per launch)",
                         l2="256 MB buffer written between steps",
                         e2e="pinned host Q/K/V/W_O copied in by every rank, fp16 [S][d] result copied out by rank 0 (it is "
                             "identical on all ranks); copy-in, compute and copy-out pipelined over row chunks",

@@ -71,6 +71,11 @@ class Weights(C.Structure):
     _fields_ = [("Qh", C.c_void_p), ("Kh", C.c_void_p), ("Vh", C.c_void_p), ("W_O", C.c_void_p)]
 
 
+class StreamGroup(C.Structure):
+    """efa_stream_group: tiles [first_tile, first_tile + ntiles) share one projection and one AllReduce."""
+    _fields_ = [("first_tile", C.c_int), ("ntiles", C.c_int)]
+
+
 class RunStats(C.Structure):
     _fields_ = [("wall_ms", C.c_double), ("attn_kernel_ms", C.c_float), ("proj_ms", C.c_float),
                 ("kernel_launches", C.c_int)]
@@ -98,12 +103,15 @@ _SIGNATURES = {
     "efa_make_params": (C.c_int, [C.POINTER(Params), C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     "efa_attn_check_params": (C.c_char_p, [C.POINTER(Params)]),
     "efa_blocks_per_tile": (C.c_int, [C.POINTER(Params)]),
+    "efa_stream_plan": (C.c_int, [C.POINTER(Params), C.POINTER(StreamGroup), C.c_int, C.POINTER(C.c_int)]),
     "efa_world_selftest": (C.c_int, [C.POINTER(WorldStruct)]),
     "efa_make_ctx": (C.c_int, [C.POINTER(C.c_void_p), C.POINTER(WorldStruct), C.c_int, C.c_int]),
     "efa_destroy_ctx": (C.c_int, [C.c_void_p]),
     "efa_fill_host_inputs": (C.c_int, [C.POINTER(Params), C.c_int, C.c_int, C.c_int,
                                        C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "efa_run_mode": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(Weights), C.c_void_p, C.POINTER(Params), C.POINTER(RunStats)]),
+    "efa_run_mode_residual": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(Weights), C.c_void_p, C.c_void_p, C.POINTER(Params),
+                                        C.POINTER(RunStats)]),
     "efa_run_mode_host": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                     C.c_void_p, C.POINTER(Params), C.POINTER(RunStats)]),
 }
@@ -183,6 +191,16 @@ def flash_attn_tc_check_params(fp: FlashParams, q_rows: int) -> Optional[str]:
 def blocks_per_tile(p: Params) -> int:
     """blocks_per_tile (attn_main.cu:275-280): (tile / 64) * H_local * split."""
     return lib().efa_blocks_per_tile(C.byref(p))
+
+
+def stream_plan(p: Params):
+    """Launch plan of stream mode (NCCL reduction): ([(first_tile, ntiles), ...], band_rows). Host arithmetic."""
+    groups = (StreamGroup * max(1, p.num_tiles))()
+    band = C.c_int(0)
+    n = lib().efa_stream_plan(C.byref(p), groups, p.num_tiles, C.byref(band))
+    if n < 0:
+        raise EfaError(f"stream_plan failed: {last_error()}")
+    return [(groups[i].first_tile, groups[i].ntiles) for i in range(n)], band.value
 
 
 def mode_name(mode: int) -> str:
@@ -365,6 +383,15 @@ def run_mode(ctx: Ctx, mode: int, w: Weights, output, p: Params) -> RunStats:
     st = RunStats()
     _check(lib().efa_run_mode(ctx.handle, mode, C.byref(w), _ptr(output), C.byref(p), C.byref(st)),
            f"run_mode({MODE_NAMES[mode] if 0 <= mode < 7 else mode})")
+    return st
+
+
+def run_mode_residual(ctx: Ctx, mode: int, w: Weights, residual, output, p: Params) -> RunStats:
+    """The block plus the step after it: ``output = residual + reduced`` with the residual (fp16 [S][d] on the
+    device) added to each reduced group of rows as it lands."""
+    st = RunStats()
+    _check(lib().efa_run_mode_residual(ctx.handle, mode, C.byref(w), _ptr(residual), _ptr(output), C.byref(p), C.byref(st)),
+           f"run_mode_residual({MODE_NAMES[mode] if 0 <= mode < 7 else mode})")
     return st
 
 

@@ -79,7 +79,7 @@ static void usage(const char* prog)
         "          [--nbuf 2] [--split 1] [--ncomm 1] [--warmup 3] [--trials 10]\n"
         "          [--modes attn,attn_tiled,megatron,sync,overlap,stream,comm] [--no-header]\n"
         "          [--causal] [--proj fp16] [--no_prio] [--no_proj] [--no_comm]\n"
-        "          [--reduce nccl|p2p] [--group_tiles 0] [--data normal|ref] [--seed 42]\n", prog);
+        "          [--reduce nccl|p2p] [--group_tiles 0] [--data normal|ref] [--seed 42] [--residual]\n", prog);
 }
 
 int main(int argc, char** argv)
@@ -171,6 +171,14 @@ int main(int argc, char** argv)
     CUDA_OK(cudaMemcpy(dw.Vh, hv.data(), qkv_n * 2, cudaMemcpyHostToDevice));
     CUDA_OK(cudaMemcpy(dw.W_O, hw.data(), wo_n * 2, cudaMemcpyHostToDevice));
 
+    // --residual: time the block together with the step after it (output = residual + block, the residual
+    // added to each reduced group of rows as it lands); modes without a block output run as usual.
+    void* residual = nullptr;
+    if (has_flag(argc, argv, "--residual")) {
+        CUDA_OK(cudaMalloc(&residual, out_n * 2));
+        CUDA_OK(cudaMemset(residual, 0x2c, out_n * 2));          // every element 0x2c2c = 0.0652
+    }
+
     if (g_rank == 0 && header)
         printf("S,H,d_h,causal,R,kernel,tile,nbuf,split,ncomm,proj,mode,min_ms,max_ms,mean_ms,median_ms,std_ms,"
                "tokens_per_s,attn_kernel_ms,reduce,data\n");
@@ -178,7 +186,9 @@ int main(int argc, char** argv)
         std::vector<double> times, attn;
         for (int t = 0; t < warmup + trials; t++) {
             efa_run_stats st;
-            EFA_OK(efa_run_mode(ctx, mode, &dw, output, &p, &st));
+            const bool block_output = mode != EFA_MODE_ATTN && mode != EFA_MODE_ATTN_TILED && mode != EFA_MODE_COMM;
+            if (residual && block_output) EFA_OK(efa_run_mode_residual(ctx, mode, &dw, residual, output, &p, &st));
+            else EFA_OK(efa_run_mode(ctx, mode, &dw, output, &p, &st));
             if (t >= warmup) { times.push_back(st.wall_ms); attn.push_back(st.attn_kernel_ms); }
         }
         int status[4] = {0, 0, 0, 0};
@@ -196,7 +206,7 @@ int main(int argc, char** argv)
             fflush(stdout);
         }
     }
-    cudaFree(dw.Qh); cudaFree(dw.Kh); cudaFree(dw.Vh); cudaFree(dw.W_O); cudaFree(output);
+    cudaFree(dw.Qh); cudaFree(dw.Kh); cudaFree(dw.Vh); cudaFree(dw.W_O); cudaFree(output); cudaFree(residual);
     EFA_OK(efa_destroy_ctx(ctx));
     MPI_Finalize();
     return 0;

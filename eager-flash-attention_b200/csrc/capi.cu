@@ -94,6 +94,13 @@ extern "C" int efa_run_mode(efa_ctx* ctx, int mode, const efa_weights* w, void* 
     return run_mode_impl(ctx, mode, *w, output, *p, stats);
 }
 
+extern "C" int efa_run_mode_residual(efa_ctx* ctx, int mode, const efa_weights* w, const void* residual, void* output,
+                                     const efa_params* p, efa_run_stats* stats)
+{
+    if (!ctx || !w || !p || !residual) { set_error("efa_run_mode_residual: null argument"); return 2; }
+    return run_mode_impl(ctx, mode, *w, output, *p, stats, residual);
+}
+
 extern "C" int efa_run_mode_host(efa_ctx* c, int mode,
                                  const uint16_t* Qh, const uint16_t* Kh, const uint16_t* Vh, const uint16_t* W_O,
                                  uint16_t* output, const efa_params* p, efa_run_stats* stats)
@@ -108,7 +115,7 @@ extern "C" int efa_run_mode_host(efa_ctx* c, int mode,
         c->h_qkv_bytes = a < b ? (a < d ? a : d) : (b < d ? b : d);
         if (ensure_bytes(&c->h_W, &c->h_w_bytes, wb) || ensure_bytes(&c->h_out, &c->h_out_bytes, ob)) return 1;
     }
-    if (mode == EFA_MODE_STREAM && p->causal && p->split == 1 && !p->skip_proj && p->reduce == EFA_REDUCE_NCCL) {
+    if (mode == EFA_MODE_STREAM && p->causal && !p->skip_proj && p->reduce == EFA_REDUCE_NCCL) {
         // copy-in, compute and copy-out overlap chunk by chunk
         efa_weights dev{c->h_Q, c->h_K, c->h_V, c->h_W};
         return run_stream_host_pipelined(c, Qh, Kh, Vh, W_O, output, dev, c->h_out, *p, stats);

@@ -20,6 +20,8 @@ struct FaArgs {
     int     tile_rows;
     int*    status;
     int     band_blocks;    // two-tile kernel: 256-row blocks per band of the work order (0 or 1 = strict row order)
+    int     heavy_first;    // two-tile kernel: take the row blocks (or bands) from the last to the first; with a causal
+                            // mask the last rows sweep the most keys, so the longest items start first
 };
 
 __device__ __forceinline__ float ex2(float x)

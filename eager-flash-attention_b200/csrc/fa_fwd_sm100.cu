@@ -473,6 +473,9 @@ int fa_forward(const void* Q, const void* K, const void* V, void* O, int o_dtype
     a.tile_counters = tile_counters; a.tile_rows = tile_rows;
     a.status = kernel_status_word();
     a.band_blocks = (tile_counters == nullptr) ? (q_rows + 255) / 256 : band_rows / 256;
+    // Nobody waits for particular rows of a launch without counters, so under a causal mask its longest work
+    // items (the last rows) go first and the launch ends on short ones; with counters rows complete in order.
+    a.heavy_first = (tile_counters == nullptr && p.causal && getenv("EFA_ATTN_ROW_ORDER") == nullptr) ? 1 : 0;
 
     const bool f16 = (o_dtype == EFA_F16);
     // d_h = 64 / 128 run on the warp-specialised two-tile kernel; EFA_ATTN_ONE_TILE=1 (a diagnostics
@@ -607,6 +610,7 @@ int fa_forward_noalloc(const void* Q, const void* K, const void* V, void* O, int
     a.tile_counters = nullptr; a.tile_rows = 0;
     a.status = nullptr;                      // the status word of the other entry points is allocated memory
     a.band_blocks = 0;
+    a.heavy_first = 0;
 
     dim3 grid(p.H_local * p.split, (q_rows + FA_BM - 1) / FA_BM);
     const bool f16 = (o_dtype == EFA_F16);

@@ -182,6 +182,9 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ,
             if (b >= full) { b = full; rem = item - full * per_band; nb = items_y - full * band; }
             item_x = rem / nb;
             item_y = b * band + rem % nb;
+            // Longest items first: list scheduling then ends on the shortest items instead of the longest, which
+            // is worth up to one item's duration (a fifth of the launch with four heads per GPU at 32k rows).
+            if (a.heavy_first) item_y = items_y - 1 - item_y;
         }
         it.head  = item_x % a.H_local;
         it.split = item_x / a.H_local;

@@ -231,6 +231,42 @@ extern "C" int efa_blocks_per_tile(const efa_params* p)
     return (p->tile / 64) * p->H_local * p->split;
 }
 
+extern "C" int efa_stream_plan(const efa_params* p, efa_stream_group* groups, int capacity, int* band_rows)
+{
+    if (!p || p->tile <= 0 || p->num_tiles <= 0) { set_error("efa_stream_plan: invalid params"); return -1; }
+    const bool auto_groups = p->group_tiles <= 0;
+    int gt = p->group_tiles;
+    if (auto_groups) { gt = (p->S / 8) / p->tile; if (gt < 1) gt = 1; }
+    if (gt > p->num_tiles) gt = p->num_tiles;
+    int n = 0;
+    for (int t0 = 0; t0 < p->num_tiles; n++) {
+        int nt = (t0 + gt <= p->num_tiles) ? gt : p->num_tiles - t0;
+        if (auto_groups && gt >= 4 && t0 + gt >= p->num_tiles) {
+            // the last eighth: S/16, S/32, S/32 rows
+            const int left = p->num_tiles - t0;
+            nt = (left > gt / 2) ? gt / 2 : (left > gt / 4 ? left - gt / 4 : left);
+            if (nt < 1) nt = left;
+        }
+        if (groups) {
+            if (n >= capacity) { set_error("efa_stream_plan: more than %d groups", capacity); return -1; }
+            groups[n].first_tile = t0;
+            groups[n].ntiles = nt;
+        }
+        t0 += nt;
+    }
+    if (band_rows) {
+        // Rows only have to complete group by group, so the attention kernel may order its work in bands no
+        // longer than the smallest group: S/16 rows with automatic grouping (the two smallest groups then
+        // complete together), at most 2048, whole 256-row blocks, and no bands below 512 rows.
+        int b = auto_groups ? p->S / 16 : p->group_tiles * p->tile;
+        b = (b / 256) * 256;
+        if (b > 2048) b = 2048;
+        if (b < 512) b = 0;
+        *band_rows = b;
+    }
+    return n;
+}
+
 extern "C" int efa_make_ctx(efa_ctx** out, const efa_world* world, int ncomm, int prioritize)
 {
     if (!out || !world) { set_error("efa_make_ctx: null argument"); return 2; }

@@ -47,7 +47,9 @@ int world_max(const efa_world& w, double* v);
 int ensure_bytes(void** ptr, size_t* have, size_t want);
 int ensure_events(efa_ctx* c, size_t n);
 
-int run_mode_impl(efa_ctx* c, int mode, const efa_weights& w, void* output, const efa_params& p, efa_run_stats* stats);
+// residual (optional, fp16 [S][d]): added to every reduced group of rows right after its reduction.
+int run_mode_impl(efa_ctx* c, int mode, const efa_weights& w, void* output, const efa_params& p, efa_run_stats* stats,
+                  const void* residual = nullptr);
 
 // Stream mode on HOST buffers as a pipeline over row chunks (causal, split == 1): the copy-in of chunk c+1,
 // the attention / projection / AllReduce of chunk c and the copy-out of chunk c-1 overlap. `dev` holds the

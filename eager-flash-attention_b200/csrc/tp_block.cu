@@ -12,6 +12,7 @@
 #include <chrono>
 #include <cstring>
 #include <thread>
+#include <vector>
 
 namespace efa {
 
@@ -25,10 +26,43 @@ double now_ms()
     return duration<double, std::milli>(steady_clock::now().time_since_epoch()).count();
 }
 
+// Consumer of a reduced group of rows, the step after the block: out += residual (fp16, one rounding),
+// eight elements per thread and iteration. HBM-bound: 6 bytes per element.
+__global__ void __launch_bounds__(256)
+add_residual_kernel(__half* __restrict__ out, const __half* __restrict__ residual, size_t n8)
+{
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += stride) {
+        uint4 o = reinterpret_cast<uint4*>(out)[i];
+        const uint4 r = __ldg(reinterpret_cast<const uint4*>(residual) + i);
+        __half2* oh = reinterpret_cast<__half2*>(&o);
+        const __half2* rh = reinterpret_cast<const __half2*>(&r);
+        #pragma unroll
+        for (int q = 0; q < 4; q++) oh[q] = __hadd2(oh[q], rh[q]);
+        reinterpret_cast<uint4*>(out)[i] = o;
+    }
+}
+
+int add_residual(__half* out, const __half* residual, size_t n, cudaStream_t stream)
+{
+    const size_t n8 = n / 8;                       // n = rows * d and d is a multiple of 64
+    if (n8 == 0) return 0;
+    int dev = 0, sms = 148;
+    EFA_CUDA(cudaGetDevice(&dev));
+    EFA_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    size_t blocks = (n8 + 255) / 256;
+    if (blocks > (size_t)sms * 8) blocks = (size_t)sms * 8;
+    add_residual_kernel<<<(unsigned)blocks, 256, 0, stream>>>(out, residual, n8);
+    EFA_CUDA(cudaGetLastError());
+    return 0;
+}
+
 struct Run {
     efa_ctx* c;
     const efa_weights& w;
     const efa_params& p;
+    const __half* residual = nullptr;   // optional [S][d]: added to each reduced group of rows as it lands
+    const __half* out_base = nullptr;   // the output buffer `residual` runs parallel to
     int launches = 0;
 
     efa_flash_partials ws(int rows) const
@@ -39,10 +73,16 @@ struct Run {
     }
 
     // Attention kernel only (launch_attention_raw, attn_main.cu:234-245).
+    // ws_row0: workspace row that the launch's first row maps to (split partials of several launches side by side).
     int attention_raw(__half* O, int ws_rows, int q_start, int q_rows, cudaStream_t s, int* counters, int tile_rows,
-                      int reserve_sms = 0, int band_rows = 0)
+                      int reserve_sms = 0, int band_rows = 0, int ws_row0 = 0)
     {
         efa_flash_partials q = ws(ws_rows);
+        if (q.O_part && ws_row0 > 0) {
+            q.O_part += (size_t)ws_row0 * p.d_local;
+            q.m_part += (size_t)ws_row0 * p.H_local;
+            q.l_part += (size_t)ws_row0 * p.H_local;
+        }
         launches++;
         return fa_forward(w.Qh, w.Kh, w.Vh, O, EFA_F16, &q, q_start, q_rows, p.flash_tc, s, counters, tile_rows, reserve_sms,
                           band_rows);
@@ -74,6 +114,11 @@ struct Run {
         if (!nccl) return 1;
         ncclResult_t r = nccl->AllReduce(send, recv, n, ncclHalf, ncclSum, c->nccls[slot], c->comm_streams[slot]);
         if (r != ncclSuccess) { set_error("ncclAllReduce: %s", nccl->GetErrorString(r)); return 1; }
+        if (residual) {
+            // consume the rows where they landed, on the stream that reduced them
+            launches++;
+            return add_residual(recv, residual + (recv - out_base), n, c->comm_streams[slot]);
+        }
         return 0;
     }
 };
@@ -280,6 +325,15 @@ int run_stream(Run& r, __half* output, efa_run_stats* st)
     const int target = efa_blocks_per_tile(&p);
     cudaEvent_t reset_done = c->events[p.num_tiles];
     const bool fused = (p.reduce == EFA_REDUCE_P2P) && !p.skip_comm && !p.skip_proj;
+    // Launch plan (efa_stream_plan): groups of consecutive tiles per projection + AllReduce launch, and the band
+    // of rows within which the attention kernel may reorder its work (better K/V reuse in L2 than strict row
+    // order). Measured (benchmark shape, one rank, ms per block): strict order 10.4, bands of 1024 / 2048 /
+    // 4096 / 8192 rows 10.0 / 9.6 / 9.8 / 9.7.
+    std::vector<efa_stream_group> groups(p.num_tiles);
+    int band_rows = 0;
+    const int ngroups = efa_stream_plan(&p, groups.data(), p.num_tiles, &band_rows);
+    if (ngroups < 0) return 1;
+    if (const char* e = getenv("EFA_BAND_ROWS")) band_rows = atoi(e);
     if (fused) {
         // One persistent kernel does projection and reduction of every tile beside the attention kernel:
         // it polls the tile counters itself, so nothing is enqueued per tile. The attention kernel is
@@ -294,6 +348,11 @@ int run_stream(Run& r, __half* output, efa_run_stats* st)
         if (r.attention_raw(O_all, p.S, 0, p.S, c->compute_stream, p2p_counters(c), p.tile)) return 1;
         EFA_CUDA(cudaEventRecord(c->ev_t1, c->compute_stream));
         if (p2p_tile(c, p, r.w, O_all, 0, &r.launches)) return 1;
+        if (r.residual) {
+            // the persistent kernel ends when every row block of this rank's output has been written
+            r.launches++;
+            if (add_residual(output, r.residual, (size_t)p.S * p.d, c->proj_stream)) return 1;
+        }
         if (sync_stream(c, c->compute_stream, nullptr, 0)) return 1;
         if (sync_stream(c, c->proj_stream, nullptr, 0)) return 1;
         return finish_timing(c, t0f, st, true, false, r.launches);
@@ -312,16 +371,6 @@ int run_stream(Run& r, __half* output, efa_run_stats* st)
     int reserve = 0;
     if (const char* e = getenv("EFA_RESERVE_SMS")) reserve = atoi(e);
     EFA_CUDA(cudaEventRecord(c->ev_t0, c->compute_stream));
-    // Rows only have to complete group by group, so the attention kernel may order its work in bands no
-    // longer than the smallest group (better K/V reuse in L2 than strict row order).
-    // Measured (benchmark shape, one rank, ms per block): strict order 10.4, bands of 1024 / 2048 / 4096 / 8192
-    // rows 10.0 / 9.6 / 9.8 / 9.7. With automatic grouping the band is S/16 rows (at most 2048): the two
-    // smallest groups at the end then complete together.
-    int band_rows = (p.group_tiles > 0) ? p.group_tiles * p.tile : p.S / 16;
-    band_rows = (band_rows / 256) * 256;
-    if (band_rows > 2048) band_rows = 2048;
-    if (band_rows < 512) band_rows = 0;
-    if (const char* e = getenv("EFA_BAND_ROWS")) band_rows = atoi(e);
     if (r.attention_raw(O_all, p.S, 0, p.S, c->compute_stream, counters, p.tile, reserve, band_rows)) return 1;
     EFA_CUDA(cudaEventRecord(c->ev_t1, c->compute_stream));
 
@@ -334,18 +383,8 @@ int run_stream(Run& r, __half* output, efa_run_stats* st)
     // Automatic grouping: S/8 rows per group, except that the last eighth of the rows is cut into
     // S/16, S/32 and S/32: what is still exposed after the attention kernel ends is the projection and
     // the collective of the last group, so that one should be small.
-    const bool auto_groups = p.group_tiles <= 0;
-    int gt = p.group_tiles;
-    if (auto_groups) { gt = (p.S / 8) / p.tile; if (gt < 1) gt = 1; }
-    if (gt > p.num_tiles) gt = p.num_tiles;
-    int gidx = 0;
-    for (int t0g = 0; t0g < p.num_tiles; gidx++) {
-        int nt = (t0g + gt <= p.num_tiles) ? gt : p.num_tiles - t0g;
-        if (auto_groups && gt >= 4 && t0g + gt >= p.num_tiles) {
-            const int left = p.num_tiles - t0g;          // tiles of the last eighth still to place
-            nt = (left > gt / 2) ? gt / 2 : (left > gt / 4 ? left - gt / 4 : left);
-            if (nt < 1) nt = left;
-        }
+    for (int gidx = 0; gidx < ngroups; gidx++) {
+        const int t0g = groups[gidx].first_tile, nt = groups[gidx].ntiles;
         for (int t = t0g; t < t0g + nt; t++)
             EFA_CU(api->cuStreamWaitValue32((CUstream)c->proj_stream, (CUdeviceptr)(counters + t),
                                             (cuuint32_t)target, CU_STREAM_WAIT_VALUE_GEQ));
@@ -358,7 +397,6 @@ int run_stream(Run& r, __half* output, efa_run_stats* st)
         const int slot = gidx % c->ncomm;
         EFA_CUDA(cudaStreamWaitEvent(c->comm_streams[slot], c->events[gidx], 0));
         if (r.allreduce(slot, S_t, output + (size_t)t0g * p.tile * p.d, (size_t)rows * p.d)) return 1;
-        t0g += nt;
     }
     if (sync_stream(c, c->compute_stream, counters, p.num_tiles)) return 1;
     if (sync_stream(c, c->proj_stream, counters, p.num_tiles)) return 1;
@@ -389,13 +427,13 @@ int run_stream_host_pipelined(efa_ctx* c, const uint16_t* Qh, const uint16_t* Kh
 {
     const DriverApi* api = driver_api();
     if (!api) return 1;
-    if (!p.causal || p.split != 1 || p.skip_proj) { set_error("pipelined host path: causal, split == 1 only"); return 2; }
+    if (!p.causal || p.skip_proj) { set_error("pipelined host path: causal mask and projection required"); return 2; }
     if (!c->h2d_stream) EFA_CUDA(cudaStreamCreateWithFlags(&c->h2d_stream, cudaStreamNonBlocking));
     if (!c->d2h_stream) EFA_CUDA(cudaStreamCreateWithFlags(&c->d2h_stream, cudaStreamNonBlocking));
     // chunks of about S/8 rows, whole tiles
     int ct = (p.S / 8) / p.tile; if (ct < 1) ct = 1;
     const int nchunk = (p.num_tiles + ct - 1) / ct;
-    if (scratch(c, p, p.S, p.S, p.num_tiles, 0, (size_t)3 * nchunk + 2)) return 1;
+    if (scratch(c, p, p.S, p.S, p.num_tiles, p.S, (size_t)3 * nchunk + 2)) return 1;
     Run r{c, dev, p};
     __half* O_all = static_cast<__half*>(c->O_all);
     __half* send_buf = static_cast<__half*>(c->send_buf);
@@ -429,10 +467,13 @@ int run_stream_host_pipelined(efa_ctx* c, const uint16_t* Qh, const uint16_t* Kh
         EFA_CUDA(cudaEventRecord(ev_in(i), c->h2d_stream));
         // causal: rows of chunk i need keys of chunks 0..i only, and those are on the device now
         EFA_CUDA(cudaStreamWaitEvent(c->compute_stream, ev_in(i), 0));
-        if (r.attention_raw(O_all + (size_t)row0 * p.d_local, rows, row0, rows, c->compute_stream, counters + t0c, p.tile, 0,
-                            /* the chunk is consumed as a whole: */ rows >= 512 ? (rows > 2048 ? 2048 : (rows / 256) * 256) : 0)) return 1;
+        // split partials of all chunks share one [split][S] workspace, each chunk at its own rows
+        if (r.attention_raw(O_all + (size_t)row0 * p.d_local, p.S, row0, rows, c->compute_stream, counters + t0c, p.tile, 0,
+                            /* the chunk is consumed as a whole: */ rows >= 512 ? (rows > 2048 ? 2048 : (rows / 256) * 256) : 0,
+                            row0)) return 1;
         for (int t = t0c; t < t0c + nt; t++)
             EFA_CU(api->cuStreamWaitValue32((CUstream)c->proj_stream, (CUdeviceptr)(counters + t), (cuuint32_t)target, CU_STREAM_WAIT_VALUE_GEQ));
+        if (r.combine(O_all + (size_t)row0 * p.d_local, p.S, row0, rows, c->proj_stream)) return 1;
         if (r.project(O_all + (size_t)row0 * p.d_local, send_buf + (size_t)row0 * p.d, rows)) return 1;
         EFA_CUDA(cudaEventRecord(ev_proj(i), c->proj_stream));
         const int slot = i % c->ncomm;
@@ -456,15 +497,23 @@ int run_stream_host_pipelined(efa_ctx* c, const uint16_t* Qh, const uint16_t* Kh
     return finish_timing(c, t0, stats, false, false, r.launches);
 }
 
-int run_mode_impl(efa_ctx* c, int mode, const efa_weights& w, void* output, const efa_params& p, efa_run_stats* stats)
+int run_mode_impl(efa_ctx* c, int mode, const efa_weights& w, void* output, const efa_params& p, efa_run_stats* stats,
+                  const void* residual)
 {
     if (!c) { set_error("run_mode: null context"); return 2; }
     if (const char* why = efa_attn_check_params(&p)) { set_error("invalid params: %s", why); return 2; }
     if (p.R != c->world.size) { set_error("params are for %d ranks, the context has %d", p.R, c->world.size); return 2; }
     if (!w.Qh || !w.Kh || !w.Vh || !w.W_O) { set_error("run_mode: null weights"); return 2; }
     if (mode != EFA_MODE_ATTN && mode != EFA_MODE_ATTN_TILED && !output) { set_error("run_mode: null output"); return 2; }
+    if (residual && (p.skip_comm || p.skip_proj)) { set_error("run_mode: a residual needs the projection and the reduction"); return 2; }
+    if (residual && (mode == EFA_MODE_ATTN || mode == EFA_MODE_ATTN_TILED || mode == EFA_MODE_COMM)) {
+        set_error("run_mode: mode %s writes no block output to add a residual to", kModeNames[mode]);
+        return 2;
+    }
     Run r{c, w, p};
     __half* out = static_cast<__half*>(output);
+    r.residual = static_cast<const __half*>(residual);
+    r.out_base = out;
     switch (mode) {
         case EFA_MODE_ATTN:       return run_attn_only(r, stats, false);
         case EFA_MODE_ATTN_TILED: return run_attn_only(r, stats, true);

@@ -158,6 +158,17 @@ const char* efa_attn_check_params(const efa_params* p);
 /* blocks_per_tile (attn_main.cuh:68, attn_main.cu:275-280): the counter target of a tile. */
 int efa_blocks_per_tile(const efa_params* p);
 
+/* The launch plan of stream mode with the NCCL reduction (the loop of run_stream, run_drivers.cu:227-240,
+ * which there is one tile per iteration): consecutive tiles [first_tile, first_tile + ntiles) share one
+ * projection launch and one AllReduce after a cuStreamWaitValue32 on each of their counters.
+ * group_tiles > 0: groups of that many tiles (1 = the reference's schedule). group_tiles == 0: about S/8
+ * rows per group and the last eighth cut into S/16, S/32, S/32, so that what remains after the attention
+ * kernel ends is small. *band_rows (if not NULL): the band within which the attention kernel may take its
+ * work head by head instead of in strict row order, 0 = strict order. Host arithmetic only.
+ * Returns the number of groups (groups may be NULL to count them), -1 on error. */
+typedef struct efa_stream_group { int first_tile, ntiles; } efa_stream_group;
+int efa_stream_plan(const efa_params* p, efa_stream_group* groups, int capacity, int* band_rows);
+
 /* Host control plane of one rank. The reference uses MPI for exactly these four operations
  * (MPI_Barrier / MPI_Allreduce(MAX) / MPI_Bcast / and, new here, an all-gather of opaque bytes for
  * IPC handles); a caller supplies them over whatever it has (the bundled shared-memory shim, or
@@ -214,6 +225,16 @@ typedef struct efa_run_stats {
  * the reduced result, identical on every rank (untouched by attn / attn_tiled). Collective. */
 int efa_run_mode(efa_ctx* ctx, int mode, const efa_weights* w, void* output,
                  const efa_params* p, efa_run_stats* stats);
+
+/* The block followed by the first step after it: output = residual + (reduced projection), with the
+ * residual (fp16 [S][d] device buffer, same on every rank) added to each reduced group of rows on the
+ * stream that reduced it, as soon as it has landed — per tile group in stream / overlap / sync mode, once in
+ * megatron mode, after the persistent kernel with the fused reduction. One fp16 rounding on top of
+ * efa_run_mode's result. The reference stops at the AllReduce output buffer (run_drivers.cuh:22-24,
+ * run_drivers.cu:26-30), so this has no counterpart there. Rejected for attn, attn_tiled and comm
+ * (no block output) and with skip_proj / skip_comm. Collective. */
+int efa_run_mode_residual(efa_ctx* ctx, int mode, const efa_weights* w, const void* residual, void* output,
+                          const efa_params* p, efa_run_stats* stats);
 
 /* The whole block on HOST buffers: copies this rank's fp16 Q/K/V/W_O to the device, runs `mode`,
  * copies the fp16 [S][d] result back. The copies are inside wall_ms. Buffers should be pinned.

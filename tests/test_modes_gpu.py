@@ -94,10 +94,14 @@ def test_single_gpu_benchmark_configuration(pkg, oracle, torch_cuda, ctx, causal
         assert_close(oracle, got[rows], ref, name)
 
 
-def test_host_buffer_entry_point(pkg, oracle, torch_cuda, ctx):
+@pytest.mark.parametrize("shape", [(512, 256, 4, 128, 1), (512, 256, 4, 128, 2), (2048, 512, 4, 128, 4), (2048, 1024, 8, 256, 1)],
+                         ids=lambda c: "S%d_d%d_H%d_t%d_s%d" % c)
+def test_host_buffer_entry_point(pkg, oracle, torch_cuda, ctx, shape):
+    """Stream mode on pinned host buffers: copy-in, compute and copy-out pipelined over row chunks; with
+    split-KV every chunk's partials sit at their own rows of one workspace."""
     torch = torch_cuda
-    S, d, H, tile = 512, 256, 4, 128
-    p = pkg.make_params(S, d, H, tile, causal=1)
+    S, d, H, tile, split = shape
+    p = pkg.make_params(S, d, H, tile, split=split, causal=1)
     bits, vals = ref_inputs_f16(oracle, S, d, H, 1, 0, 123)
     ref = oracle.block_rows([vals], d, 1)
     pinned = [torch.from_numpy(b.view(np.float16)).pin_memory() for b in bits]
@@ -158,3 +162,48 @@ def test_stream_mode_with_reserved_sms(pkg, oracle, torch_cuda, ctx, case, monke
         assert pkg.kernel_status()[0] == 0, pkg.kernel_status()
         got = out.float().cpu().numpy()
         assert_close(oracle, got if rows is None else got[rows], ref, f"rep {rep}")
+
+
+@pytest.mark.parametrize("case", [(512, 256, 4, 128, 2, 1, 0), (1024, 512, 8, 128, 3, 2, 1), (2048, 1024, 8, 256, 2, 1, 1)],
+                         ids=lambda c: "S%d_d%d_H%d_t%d_n%d_s%d_c%d" % c)
+def test_residual_is_added_to_every_reduced_group(pkg, oracle, torch_cuda, ctx, case):
+    """The step after the block (the reference stops at the AllReduce output, run_drivers.cuh:22-24):
+    output = residual + block, the residual added group by group as the rows land. Checked bit for bit
+    against the same mode without a residual plus one fp16 addition (that run is checked against the CPU checker)."""
+    torch = torch_cuda
+    S, d, H, tile, nbuf, split, causal = case
+    p = pkg.make_params(S, d, H, tile, nbuf, split, causal)
+    bits, vals = ref_inputs_f16(oracle, S, d, H, 1, 0, 42)
+    ref = oracle.block_rows([vals], d, causal)
+    dev = to_dev(torch, bits)
+    w = pkg.Weights(*(t.data_ptr() for t in dev))
+    g = torch.Generator(device="cpu").manual_seed(7)
+    residual = (torch.rand((S, d), generator=g) - 0.5).to(torch.float16).cuda()
+    for name in CHECKED_MODES:
+        plain = torch.zeros((S, d), dtype=torch.float16, device="cuda")
+        pkg.run_mode(ctx, pkg.parse_mode(name), w, plain, p)
+        out = torch.full((S, d), float("nan"), dtype=torch.float16, device="cuda")
+        pkg.kernel_status_reset()
+        st = pkg.run_mode_residual(ctx, pkg.parse_mode(name), w, residual, out, p)
+        torch.cuda.synchronize()
+        assert pkg.kernel_status()[0] == 0
+        assert st.kernel_launches > 0
+        assert torch.equal(out, plain + residual), name
+        assert_close(oracle, plain.float().cpu().numpy(), ref, f"{name} without residual")
+
+
+def test_residual_is_rejected_where_no_block_output_exists(pkg, oracle, torch_cuda, ctx):
+    torch = torch_cuda
+    S, d, H, tile = 512, 256, 4, 128
+    p = pkg.make_params(S, d, H, tile)
+    bits, _ = ref_inputs_f16(oracle, S, d, H, 1, 0, 42)
+    dev = to_dev(torch, bits)
+    w = pkg.Weights(*(t.data_ptr() for t in dev))
+    out = torch.zeros((S, d), dtype=torch.float16, device="cuda")
+    res = torch.zeros((S, d), dtype=torch.float16, device="cuda")
+    for name in ("attn", "attn_tiled", "comm"):
+        with pytest.raises(pkg.EfaError, match="no block output"):
+            pkg.run_mode_residual(ctx, pkg.parse_mode(name), w, res, out, p)
+    p.skip_comm = 1
+    with pytest.raises(pkg.EfaError, match="needs the projection and the reduction"):
+        pkg.run_mode_residual(ctx, pkg.MODE_STREAM, w, res, out, p)
