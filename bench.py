@@ -327,11 +327,13 @@ def main():
                           frac=achieved / pk["tflops"], peak_source=f"of {pk['source']} (burst bf16)",
                           frac_sustained=achieved / pk["tflops_sustained"], attn_kernel_ms=attn_ms,
                           algorithmic_flops=fl,
-                          # dram__bytes_read+write of this kernel in stream mode, captured at S=8192 (0.834 GB per
-                          # launch, profiles/fa_fwd_ws_kernel_d128_S8192.md) and scaled by algorithmic FLOPs: an
-                          # estimate, the full-size launch is too long for a multi-pass capture
-                          traffic=(0.834e9 * fl / attention_flops(8192, 128, 32, 1)) if (p.causal and p.d_h == 128) else None,
-                          traffic_note="scaled from an ncu capture at S=8192 by algorithmic FLOPs (estimate)"),
+                          # dram__bytes_read.sum + dram__bytes_write.sum of this kernel's stream-mode launch at the
+                          # benchmark shape on one rank (32 heads): 4.797 GB + 0.308 GB, one ncu capture
+                          # (profiles/fa_fwd_ws_kernel_d128_S32768_traffic.md). Heads are independent, so a rank's
+                          # traffic is that figure times H_local / 32. Other shapes were not captured.
+                          traffic=(5.105e9 * p.H_local / 32 if (p.S == 32768 and p.d_h == 128 and p.causal and args.mode == "stream"
+                                                                and p.split == 1) else None),
+                          algorithmic_bytes=2.0 * p.S * p.d_local * 4),      # Q, K, V read once, O written once (fp16)
             cpu_baseline=cpu,
             e2e=dict(value=e2e_ms, unit="ms", h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h),
             gpu_launches=launches * args.steps,
