@@ -51,7 +51,7 @@ class Params(C.Structure):
                 ("tile", C.c_int), ("num_tiles", C.c_int),
                 ("nbuf", C.c_int), ("split", C.c_int), ("causal", C.c_int),
                 ("skip_proj", C.c_int), ("skip_comm", C.c_int), ("reduce", C.c_int), ("group_tiles", C.c_int),
-                ("flash_tc", FlashParams)]
+                ("proj_f32", C.c_int), ("flash_tc", FlashParams)]
 
 
 _BARRIER_FN = C.CFUNCTYPE(C.c_int, C.c_void_p)

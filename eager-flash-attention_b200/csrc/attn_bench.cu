@@ -78,7 +78,7 @@ static void usage(const char* prog)
         "usage: %s [--S 4096] [--H 16] [--d_h 64] [--tile 256] [--kernel tc]\n"
         "          [--nbuf 2] [--split 1] [--ncomm 1] [--warmup 3] [--trials 10]\n"
         "          [--modes attn,attn_tiled,megatron,sync,overlap,stream,comm] [--no-header]\n"
-        "          [--causal] [--proj fp16] [--no_prio] [--no_proj] [--no_comm]\n"
+        "          [--causal] [--proj fp16|fp32] [--no_prio] [--no_proj] [--no_comm]\n"
         "          [--reduce nccl|p2p] [--group_tiles 0] [--data normal|ref] [--seed 42] [--residual]\n", prog);
 }
 
@@ -113,11 +113,15 @@ int main(int argc, char** argv)
     const int d = H * d_h;
 
     if (std::strcmp(kernel, "tc") != 0) fail("--kernel must be tc (the scalar v1 prototype is not part of this build)");
-    if (std::strcmp(proj, "fp16") != 0) {
-        if (std::strcmp(proj, "fp32") != 0 && std::strcmp(proj, "tf32") != 0) fail("--proj must be fp16 (fp32 and tf32 are accepted and run as fp16)");
-        if (g_rank == 0) fprintf(stderr, "note: --proj %s requested; this build projects in fp16 with fp32 accumulation\n", proj);
-        proj = "fp16";
-    }
+    // --proj (attn_bench.cu:55,113-117 of the reference: fp32 | tf32 cuBLAS math). Here the operands are fp16 and the
+    // accumulator fp32 in every case; the switch picks the type of the partial sums, the reduction and the output:
+    // fp16 (default), or fp32 as in the reference. tf32 is accepted as a synonym of fp32.
+    int proj_f32 = 0;
+    if (std::strcmp(proj, "fp32") == 0 || std::strcmp(proj, "tf32") == 0) {
+        if (std::strcmp(proj, "tf32") == 0 && g_rank == 0) fprintf(stderr, "note: --proj tf32 runs as fp32 (fp16 operands, fp32 partial sums)\n");
+        proj = "fp32";
+        proj_f32 = 1;
+    } else if (std::strcmp(proj, "fp16") != 0) fail("--proj must be fp16 or fp32");
     if (trials < 1) fail("--trials must be >= 1");
 
     std::vector<int> modes;
@@ -142,6 +146,7 @@ int main(int argc, char** argv)
     p.skip_proj = has_flag(argc, argv, "--no_proj");
     p.skip_comm = has_flag(argc, argv, "--no_comm");
     p.group_tiles = arg_int(argc, argv, "--group_tiles", 0);
+    p.proj_f32 = proj_f32;
     if (std::strcmp(reduce, "p2p") == 0) p.reduce = EFA_REDUCE_P2P;
     else if (std::strcmp(reduce, "nccl") != 0) fail("--reduce must be nccl or p2p");
     if (const char* why = efa_attn_check_params(&p)) {
@@ -165,7 +170,7 @@ int main(int argc, char** argv)
     efa_weights dw;
     void* output = nullptr;
     CUDA_OK(cudaMalloc(&dw.Qh, qkv_n * 2)); CUDA_OK(cudaMalloc(&dw.Kh, qkv_n * 2)); CUDA_OK(cudaMalloc(&dw.Vh, qkv_n * 2));
-    CUDA_OK(cudaMalloc(&dw.W_O, wo_n * 2)); CUDA_OK(cudaMalloc(&output, out_n * 2));
+    CUDA_OK(cudaMalloc(&dw.W_O, wo_n * 2)); CUDA_OK(cudaMalloc(&output, out_n * (proj_f32 ? 4 : 2)));
     CUDA_OK(cudaMemcpy(dw.Qh, hq.data(), qkv_n * 2, cudaMemcpyHostToDevice));
     CUDA_OK(cudaMemcpy(dw.Kh, hk.data(), qkv_n * 2, cudaMemcpyHostToDevice));
     CUDA_OK(cudaMemcpy(dw.Vh, hv.data(), qkv_n * 2, cudaMemcpyHostToDevice));
@@ -175,6 +180,7 @@ int main(int argc, char** argv)
     // added to each reduced group of rows as it lands); modes without a block output run as usual.
     void* residual = nullptr;
     if (has_flag(argc, argv, "--residual")) {
+        if (proj_f32) fail("--residual goes with --proj fp16");
         CUDA_OK(cudaMalloc(&residual, out_n * 2));
         CUDA_OK(cudaMemset(residual, 0x2c, out_n * 2));          // every element 0x2c2c = 0.0652
     }

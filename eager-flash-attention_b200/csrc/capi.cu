@@ -106,6 +106,7 @@ extern "C" int efa_run_mode_host(efa_ctx* c, int mode,
                                  uint16_t* output, const efa_params* p, efa_run_stats* stats)
 {
     if (!c || !Qh || !Kh || !Vh || !W_O || !p) { set_error("efa_run_mode_host: null argument"); return 2; }
+    if (p->proj_f32) { set_error("efa_run_mode_host: the host-buffer path returns fp16 (proj_f32 must be 0)"); return 2; }
     const size_t qkv = (size_t)p->H_local * p->S * p->d_h * 2;
     const size_t wb = (size_t)p->d_local * p->d * 2;
     const size_t ob = (size_t)p->S * p->d * 2;

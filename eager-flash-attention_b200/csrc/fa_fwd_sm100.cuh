@@ -25,7 +25,8 @@ int fa_combine(const efa_flash_partials& part, void* O, int o_dtype, int row0, i
 
 int convert_f32_to_f16_dev(const float* in, void* out, size_t n, cudaStream_t stream);
 
-// out[rows][d] = A[rows][d_local] * W[d_local][d]; fp16 in, fp32 accumulate, fp16 out.
-int project_f16(const void* A, const void* W, void* out, int rows, int d_local, int d, cudaStream_t stream);
+// out[rows][d] = A[rows][d_local] * W[d_local][d]; fp16 in, fp32 accumulate, fp16 (EFA_F16) or fp32 (EFA_F32) out.
+int project_f16(const void* A, const void* W, void* out, int rows, int d_local, int d, cudaStream_t stream,
+                int out_dtype = EFA_F16);
 
 }  // namespace efa

@@ -1,5 +1,5 @@
 // Output projection for sm_100a: out[rows][d] = A[rows][d_local] * W[d_local][d], fp16 operands,
-// fp32 accumulation in tensor memory, fp16 result.
+// fp32 accumulation in tensor memory, fp16 result (or the fp32 accumulator itself, the reference's output type).
 //
 // Stands in for project() of eager-flash-attention (attn_main.cu:262-273), which calls cublasSgemm on
 // fp32 data. Warp-specialised: warp 0 streams A (K-major, [128 rows][64 k]) and W (MN-major,
@@ -28,12 +28,12 @@ struct PjCfg {
 };
 
 struct PjArgs {
-    __half* out;
+    void* out;          // fp16 or fp32 [M][N]
     int M, N, K;
     int* status;
 };
 
-template <int BN>
+template <int BN, bool OUT_F32>
 __global__ void __launch_bounds__(192)
 proj_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW, const PjArgs a)
 {
@@ -123,8 +123,14 @@ proj_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 tmem_ld32(taddr + c * 32, r);
                 tmem_wait_ld();
                 const int col = n0 + c * 32;
-                if (row < a.M && col < a.N) {          // N is a multiple of 64, so a 32-column chunk is all in or all out
-                    uint4* dst = reinterpret_cast<uint4*>(a.out + (size_t)row * a.N + col);
+                if (OUT_F32) {
+                    if (row < a.M && col < a.N) {
+                        uint4* dst = reinterpret_cast<uint4*>(static_cast<float*>(a.out) + (size_t)row * a.N + col);
+                        #pragma unroll
+                        for (int q = 0; q < 8; q++) dst[q] = make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
+                    }
+                } else if (row < a.M && col < a.N) {   // N is a multiple of 64, so a 32-column chunk is all in or all out
+                    uint4* dst = reinterpret_cast<uint4*>(static_cast<__half*>(a.out) + (size_t)row * a.N + col);
                     #pragma unroll
                     for (int q = 0; q < 4; q++) {
                         uint4 v;
@@ -155,7 +161,7 @@ proj_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (warp == 1) tmem_dealloc(tmem_acc, BN);
 }
 
-template <int BN>
+template <int BN, bool OUT_F32>
 int launch_proj(const CUtensorMap& ta, const CUtensorMap& tw, const PjArgs& args, cudaStream_t stream)
 {
     using C = PjCfg<BN>;
@@ -163,19 +169,20 @@ int launch_proj(const CUtensorMap& ta, const CUtensorMap& tw, const PjArgs& args
     int dev = 0;
     EFA_CUDA(cudaGetDevice(&dev));
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-        EFA_CUDA(cudaFuncSetAttribute(proj_gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+        EFA_CUDA(cudaFuncSetAttribute(proj_gemm_kernel<BN, OUT_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
         configured[dev] = true;
     }
     dim3 grid((args.N + BN - 1) / BN, (args.M + PJ_BM - 1) / PJ_BM);
-    proj_gemm_kernel<BN><<<grid, 192, C::SMEM_BYTES, stream>>>(ta, tw, args);
+    proj_gemm_kernel<BN, OUT_F32><<<grid, 192, C::SMEM_BYTES, stream>>>(ta, tw, args);
     EFA_CUDA(cudaGetLastError());
     return 0;
 }
 
 }  // namespace
 
-int project_f16(const void* A, const void* W, void* out, int rows, int d_local, int d, cudaStream_t stream)
+int project_f16(const void* A, const void* W, void* out, int rows, int d_local, int d, cudaStream_t stream, int out_dtype)
 {
+    if (out_dtype != EFA_F16 && out_dtype != EFA_F32) { set_error("project: unknown output type %d", out_dtype); return 2; }
     if (rows <= 0 || rows % 64 != 0) { set_error("project: rows (%d) must be a positive multiple of 64", rows); return 2; }
     if (d_local <= 0 || d_local % 16 != 0) { set_error("project: d_local (%d) must be a positive multiple of 16", d_local); return 2; }
     if (d <= 0 || d % 64 != 0) { set_error("project: d (%d) must be a positive multiple of 64", d); return 2; }
@@ -194,10 +201,11 @@ int project_f16(const void* A, const void* W, void* out, int rows, int d_local, 
         unsigned box[2] = {64u, 64u};
         if (make_tmap_f16(&tw, W, 2, dims, strides, box)) return 1;
     }
-    PjArgs a{static_cast<__half*>(out), rows, d, d_local, kernel_status_word()};
+    PjArgs a{out, rows, d, d_local, kernel_status_word()};
     const long tiles256 = (long)((rows + 127) / 128) * (d / 256);
-    if (d % 256 == 0 && tiles256 >= 148) return launch_proj<256>(ta, tw, a, stream);
-    return launch_proj<128>(ta, tw, a, stream);
+    const bool wide = d % 256 == 0 && tiles256 >= 148;
+    if (out_dtype == EFA_F32) return wide ? launch_proj<256, true>(ta, tw, a, stream) : launch_proj<128, true>(ta, tw, a, stream);
+    return wide ? launch_proj<256, false>(ta, tw, a, stream) : launch_proj<128, false>(ta, tw, a, stream);
 }
 
 }  // namespace efa

@@ -51,6 +51,16 @@ int ensure_events(efa_ctx* c, size_t n)
     return 0;
 }
 
+int ensure_trace_events(efa_ctx* c, size_t n)
+{
+    while (c->trace_events.size() < n) {
+        cudaEvent_t e;
+        EFA_CUDA(cudaEventCreate(&e));
+        c->trace_events.push_back(e);
+    }
+    return 0;
+}
+
 // ---------------------------------------------------------------------------------------------
 // Synthetic inputs
 // ---------------------------------------------------------------------------------------------
@@ -208,6 +218,7 @@ extern "C" int efa_make_params(efa_params* out, int S, int d, int H, int tile, i
     p.skip_proj = 0; p.skip_comm = 0;
     p.reduce = EFA_REDUCE_NCCL;
     p.group_tiles = 0;
+    p.proj_f32 = 0;
     const float scale = p.d_h > 0 ? 1.0f / sqrtf((float)p.d_h) : 0.f;
     p.flash_tc = efa_flash_params{S, p.d_h, p.H_local, split, causal, scale};
     *out = p;
@@ -331,6 +342,7 @@ extern "C" int efa_destroy_ctx(efa_ctx* c)
     if (c->compute_stream) cudaStreamDestroy(c->compute_stream);
     if (c->proj_stream) cudaStreamDestroy(c->proj_stream);
     for (cudaEvent_t e : c->events) cudaEventDestroy(e);
+    for (cudaEvent_t e : c->trace_events) cudaEventDestroy(e);
     for (cudaEvent_t e : {c->ev_t0, c->ev_t1, c->ev_t2, c->ev_t3}) if (e) cudaEventDestroy(e);
     for (void* q : {c->O_all, c->send_buf, (void*)c->counters, (void*)c->ws_O, (void*)c->ws_m, (void*)c->ws_l,
                     c->h_Q, c->h_K, c->h_V, c->h_W, c->h_out})

@@ -28,6 +28,7 @@ struct efa_ctx {
     size_t ws_O_n = 0, ws_ml_n = 0;
     std::vector<cudaEvent_t> events;                        // disable-timing events, one per tile + a few
     cudaEvent_t ev_t0 = nullptr, ev_t1 = nullptr, ev_t2 = nullptr, ev_t3 = nullptr;   // timing events
+    std::vector<cudaEvent_t> trace_events;                  // timing events of the EFA_TRACE timeline (stream mode)
 
     // Device staging of efa_run_mode_host.
     void* h_Q = nullptr; void* h_K = nullptr; void* h_V = nullptr; void* h_W = nullptr; void* h_out = nullptr;
@@ -46,6 +47,7 @@ int world_max(const efa_world& w, double* v);
 // Grow-only scratch helpers; return 0 on success.
 int ensure_bytes(void** ptr, size_t* have, size_t want);
 int ensure_events(efa_ctx* c, size_t n);
+int ensure_trace_events(efa_ctx* c, size_t n);
 
 // residual (optional, fp16 [S][d]): added to every reduced group of rows right after its reduction.
 int run_mode_impl(efa_ctx* c, int mode, const efa_weights& w, void* output, const efa_params& p, efa_run_stats* stats,

@@ -10,6 +10,7 @@
 #include "p2p_reduce.h"
 
 #include <chrono>
+#include <cstdio>
 #include <cstring>
 #include <thread>
 #include <vector>
@@ -62,8 +63,12 @@ struct Run {
     const efa_weights& w;
     const efa_params& p;
     const __half* residual = nullptr;   // optional [S][d]: added to each reduced group of rows as it lands
-    const __half* out_base = nullptr;   // the output buffer `residual` runs parallel to
+    const char*   out_base = nullptr;   // the output buffer `residual` runs parallel to
     int launches = 0;
+
+    // Partial sums and output are fp16, or fp32 with proj_f32 (the reference's types).
+    size_t esz() const { return p.proj_f32 ? sizeof(float) : sizeof(__half); }
+    size_t row_bytes() const { return (size_t)p.d * esz(); }
 
     efa_flash_partials ws(int rows) const
     {
@@ -100,24 +105,26 @@ struct Run {
         return combine(O, ws_rows, 0, q_rows, s);
     }
     // project (attn_main.cu:262-273) on the projection stream.
-    int project(const __half* O_tile, __half* out, int rows)
+    int project(const __half* O_tile, void* out, int rows)
     {
         if (p.skip_proj) return 0;
         launches++;
-        return project_f16(O_tile, w.W_O, out, rows, p.d_local, p.d, c->proj_stream);
+        return project_f16(O_tile, w.W_O, out, rows, p.d_local, p.d, c->proj_stream, p.proj_f32 ? EFA_F32 : EFA_F16);
     }
-    // allreduce (run_drivers.cu:26-30): communicator slot `slot`, fp16 sum.
-    int allreduce(int slot, const __half* send, __half* recv, size_t n)
+    // allreduce (run_drivers.cu:26-30): communicator slot `slot`, sum of n elements (fp16, or fp32 with proj_f32).
+    int allreduce(int slot, const void* send, void* recv, size_t n)
     {
         if (p.skip_comm) return 0;
         const NcclApi* nccl = nccl_api();
         if (!nccl) return 1;
-        ncclResult_t r = nccl->AllReduce(send, recv, n, ncclHalf, ncclSum, c->nccls[slot], c->comm_streams[slot]);
+        ncclResult_t r = nccl->AllReduce(send, recv, n, p.proj_f32 ? ncclFloat : ncclHalf, ncclSum, c->nccls[slot],
+                                         c->comm_streams[slot]);
         if (r != ncclSuccess) { set_error("ncclAllReduce: %s", nccl->GetErrorString(r)); return 1; }
         if (residual) {
             // consume the rows where they landed, on the stream that reduced them
             launches++;
-            return add_residual(recv, residual + (recv - out_base), n, c->comm_streams[slot]);
+            const size_t first = (size_t)(static_cast<const char*>(recv) - out_base) / sizeof(__half);   // fp16 output only
+            return add_residual(static_cast<__half*>(recv), residual + first, n, c->comm_streams[slot]);
         }
         return 0;
     }
@@ -178,7 +185,7 @@ int finish_timing(efa_ctx* c, double t0, efa_run_stats* st, bool attn_events, bo
 int scratch(efa_ctx* c, const efa_params& p, size_t o_rows, size_t send_rows, size_t ncounters, size_t ws_rows, size_t nevents)
 {
     if (o_rows && ensure_bytes(&c->O_all, &c->O_all_bytes, o_rows * p.d_local * sizeof(__half))) return 1;
-    if (send_rows && ensure_bytes(&c->send_buf, &c->send_bytes, send_rows * p.d * sizeof(__half))) return 1;
+    if (send_rows && ensure_bytes(&c->send_buf, &c->send_bytes, send_rows * p.d * (p.proj_f32 ? sizeof(float) : sizeof(__half)))) return 1;
     if (ncounters) {
         size_t have = c->counters_n * sizeof(int);
         if (ensure_bytes((void**)&c->counters, &have, ncounters * sizeof(int))) return 1;
@@ -221,12 +228,12 @@ int run_attn_only(Run& r, efa_run_stats* st, bool tiled)
 }
 
 // run_megatron (run_drivers.cu:72-106)
-int run_megatron(Run& r, __half* output, efa_run_stats* st)
+int run_megatron(Run& r, char* output, efa_run_stats* st)
 {
     efa_ctx* c = r.c; const efa_params& p = r.p;
     if (scratch(c, p, p.S, p.S, 0, p.S, 2)) return 1;
     __half* O_all = static_cast<__half*>(c->O_all);
-    __half* send_buf = static_cast<__half*>(c->send_buf);
+    char* send_buf = static_cast<char*>(c->send_buf);
     cudaEvent_t attn_done = c->events[0], proj_done = c->events[1];
 
     if (world_barrier(c->world)) return 1;
@@ -249,12 +256,12 @@ int run_megatron(Run& r, __half* output, efa_run_stats* st)
 }
 
 // run_sync (run_drivers.cu:108-136)
-int run_sync(Run& r, __half* output, efa_run_stats* st)
+int run_sync(Run& r, char* output, efa_run_stats* st)
 {
     efa_ctx* c = r.c; const efa_params& p = r.p;
     if (scratch(c, p, p.tile, p.tile, 0, p.tile, 0)) return 1;
     __half* O_tile = static_cast<__half*>(c->O_all);
-    __half* send_buf = static_cast<__half*>(c->send_buf);
+    char* send_buf = static_cast<char*>(c->send_buf);
     if (world_barrier(c->world)) return 1;
     const double t0 = now_ms();
     for (int t = 0; t < p.num_tiles; t++) {
@@ -262,7 +269,7 @@ int run_sync(Run& r, __half* output, efa_run_stats* st)
         if (sync_stream(c, c->compute_stream, nullptr, 0)) return 1;
         if (r.project(O_tile, send_buf, p.tile)) return 1;
         if (sync_stream(c, c->proj_stream, nullptr, 0)) return 1;
-        if (r.allreduce(0, send_buf, output + (size_t)t * p.tile * p.d, (size_t)p.tile * p.d)) return 1;
+        if (r.allreduce(0, send_buf, output + (size_t)t * p.tile * r.row_bytes(), (size_t)p.tile * p.d)) return 1;
         if (sync_stream(c, c->comm_streams[0], nullptr, 0)) return 1;
     }
     return finish_timing(c, t0, st, false, false, r.launches);
@@ -272,13 +279,13 @@ int run_sync(Run& r, __half* output, efa_run_stats* st)
 //   compute: attn(t)  waits proj_done(t - nbuf)            (O buffer b free)
 //   proj:    gemm(t)  waits attn_done(t), comm_done(t - nbuf)   (send buffer b free)
 //   comm[t % ncomm]: allreduce(t) waits proj_done(t)
-int run_overlap(Run& r, __half* output, efa_run_stats* st)
+int run_overlap(Run& r, char* output, efa_run_stats* st)
 {
     efa_ctx* c = r.c; const efa_params& p = r.p;
     const int nbuf = p.nbuf;
     if (scratch(c, p, (size_t)nbuf * p.tile, (size_t)nbuf * p.tile, 0, p.tile, (size_t)3 * nbuf)) return 1;
     __half* O_buf = static_cast<__half*>(c->O_all);
-    __half* S_buf = static_cast<__half*>(c->send_buf);
+    char* S_buf = static_cast<char*>(c->send_buf);
     auto attn_done = [&](int b) { return c->events[3 * b]; };
     auto proj_done = [&](int b) { return c->events[3 * b + 1]; };
     auto comm_done = [&](int b) { return c->events[3 * b + 2]; };
@@ -288,7 +295,7 @@ int run_overlap(Run& r, __half* output, efa_run_stats* st)
     for (int t = 0; t < p.num_tiles; t++) {
         const int b = t % nbuf;
         __half* O_t = O_buf + (size_t)b * p.tile * p.d_local;
-        __half* S_t = S_buf + (size_t)b * p.tile * p.d;
+        char* S_t = S_buf + (size_t)b * p.tile * r.row_bytes();
         if (t >= nbuf) EFA_CUDA(cudaStreamWaitEvent(c->compute_stream, proj_done(b), 0));
         if (r.attention(O_t, p.tile, t * p.tile, p.tile, c->compute_stream)) return 1;
         EFA_CUDA(cudaEventRecord(attn_done(b), c->compute_stream));
@@ -300,7 +307,7 @@ int run_overlap(Run& r, __half* output, efa_run_stats* st)
 
         const int slot = t % c->ncomm;
         EFA_CUDA(cudaStreamWaitEvent(c->comm_streams[slot], proj_done(b), 0));
-        if (r.allreduce(slot, S_t, output + (size_t)t * p.tile * p.d, (size_t)p.tile * p.d)) return 1;
+        if (r.allreduce(slot, S_t, output + (size_t)t * p.tile * r.row_bytes(), (size_t)p.tile * p.d)) return 1;
         EFA_CUDA(cudaEventRecord(comm_done(b), c->comm_streams[slot]));
     }
     if (sync_stream(c, c->compute_stream, nullptr, 0)) return 1;
@@ -313,14 +320,14 @@ int run_overlap(Run& r, __half* output, efa_run_stats* st)
 // 64-row blocks per tile; the projection stream holds, for every tile, a front-end wait on that
 // tile's counter (cuStreamWaitValue32, no SM involved), the split combine, the projection and an
 // event; the tile's AllReduce follows on communicator t % ncomm.
-int run_stream(Run& r, __half* output, efa_run_stats* st)
+int run_stream(Run& r, char* output, efa_run_stats* st)
 {
     efa_ctx* c = r.c; const efa_params& p = r.p;
     const DriverApi* api = driver_api();
     if (!api) return 1;
     if (scratch(c, p, p.S, p.S, p.num_tiles, p.S, (size_t)p.num_tiles + 1)) return 1;
     __half* O_all = static_cast<__half*>(c->O_all);
-    __half* send_buf = static_cast<__half*>(c->send_buf);
+    char* send_buf = static_cast<char*>(c->send_buf);
     int* counters = c->counters;
     const int target = efa_blocks_per_tile(&p);
     cudaEvent_t reset_done = c->events[p.num_tiles];
@@ -334,6 +341,11 @@ int run_stream(Run& r, __half* output, efa_run_stats* st)
     const int ngroups = efa_stream_plan(&p, groups.data(), p.num_tiles, &band_rows);
     if (ngroups < 0) return 1;
     if (const char* e = getenv("EFA_BAND_ROWS")) band_rows = atoi(e);
+    // EFA_TRACE=1: timing events around every group (counters reached, projection done, reduction done) and a
+    // timeline on stderr after the run, relative to the start of the attention kernel. Diagnostic; the events
+    // cost a few microseconds each, so traced runs are not benchmark numbers.
+    const bool trace = getenv("EFA_TRACE") != nullptr && !fused;
+    if (trace && ensure_trace_events(c, (size_t)3 * ngroups)) return 1;
     if (fused) {
         // One persistent kernel does projection and reduction of every tile beside the attention kernel:
         // it polls the tile counters itself, so nothing is enqueued per tile. The attention kernel is
@@ -351,7 +363,7 @@ int run_stream(Run& r, __half* output, efa_run_stats* st)
         if (r.residual) {
             // the persistent kernel ends when every row block of this rank's output has been written
             r.launches++;
-            if (add_residual(output, r.residual, (size_t)p.S * p.d, c->proj_stream)) return 1;
+            if (add_residual(reinterpret_cast<__half*>(output), r.residual, (size_t)p.S * p.d, c->proj_stream)) return 1;
         }
         if (sync_stream(c, c->compute_stream, nullptr, 0)) return 1;
         if (sync_stream(c, c->proj_stream, nullptr, 0)) return 1;
@@ -390,32 +402,49 @@ int run_stream(Run& r, __half* output, efa_run_stats* st)
                                             (cuuint32_t)target, CU_STREAM_WAIT_VALUE_GEQ));
         const int rows = nt * p.tile;
         __half* O_t = O_all + (size_t)t0g * p.tile * p.d_local;
-        __half* S_t = send_buf + (size_t)t0g * p.tile * p.d;
+        char* S_t = send_buf + (size_t)t0g * p.tile * r.row_bytes();
+        if (trace) EFA_CUDA(cudaEventRecord(c->trace_events[3 * gidx], c->proj_stream));
         if (r.combine(O_t, p.S, t0g * p.tile, rows, c->proj_stream)) return 1;
         if (r.project(O_t, S_t, rows)) return 1;
         EFA_CUDA(cudaEventRecord(c->events[gidx], c->proj_stream));
+        if (trace) EFA_CUDA(cudaEventRecord(c->trace_events[3 * gidx + 1], c->proj_stream));
         const int slot = gidx % c->ncomm;
         EFA_CUDA(cudaStreamWaitEvent(c->comm_streams[slot], c->events[gidx], 0));
-        if (r.allreduce(slot, S_t, output + (size_t)t0g * p.tile * p.d, (size_t)rows * p.d)) return 1;
+        if (r.allreduce(slot, S_t, output + (size_t)t0g * p.tile * r.row_bytes(), (size_t)rows * p.d)) return 1;
+        if (trace) EFA_CUDA(cudaEventRecord(c->trace_events[3 * gidx + 2], c->comm_streams[slot]));
     }
+    const double t_enqueued = now_ms() - t0;
     if (sync_stream(c, c->compute_stream, counters, p.num_tiles)) return 1;
     if (sync_stream(c, c->proj_stream, counters, p.num_tiles)) return 1;
     if (sync_comm_streams(c)) return 1;
-    return finish_timing(c, t0, st, true, false, r.launches);
+    const int rc = finish_timing(c, t0, st, true, false, r.launches);
+    if (trace && rc == 0) {
+        float attn_end = 0.f;
+        EFA_CUDA(cudaEventElapsedTime(&attn_end, c->ev_t0, c->ev_t1));
+        fprintf(stderr, "efa trace rank %d: host enqueue done at %.3f ms after the barrier; attention kernel 0 .. %.3f ms\n",
+                c->world.rank, t_enqueued, attn_end);
+        for (int g = 0; g < ngroups; g++) {
+            float t[3] = {0.f, 0.f, 0.f};
+            for (int k = 0; k < 3; k++) EFA_CUDA(cudaEventElapsedTime(&t[k], c->ev_t0, c->trace_events[3 * g + k]));
+            fprintf(stderr, "efa trace rank %d: rows %6d..%6d  counters reached %.3f  projected %.3f  reduced %.3f ms\n",
+                    c->world.rank, groups[g].first_tile * p.tile, (groups[g].first_tile + groups[g].ntiles) * p.tile, t[0], t[1], t[2]);
+        }
+    }
+    return rc;
 }
 
 // run_comm_only (run_drivers.cu:259-275): the per-tile AllReduces of a full pass, back to back on
 // communicator 0; sweeping the tile size gives t_allreduce(bytes).
-int run_comm_only(Run& r, __half* output, efa_run_stats* st)
+int run_comm_only(Run& r, char* output, efa_run_stats* st)
 {
     efa_ctx* c = r.c; const efa_params& p = r.p;
     if (scratch(c, p, 0, p.S, 0, 0, 0)) return 1;
-    __half* send_buf = static_cast<__half*>(c->send_buf);
-    EFA_CUDA(cudaMemset(send_buf, 0, (size_t)p.S * p.d * sizeof(__half)));
+    char* send_buf = static_cast<char*>(c->send_buf);
+    EFA_CUDA(cudaMemset(send_buf, 0, (size_t)p.S * r.row_bytes()));
     if (world_barrier(c->world)) return 1;
     const double t0 = now_ms();
     for (int t = 0; t < p.num_tiles; t++)
-        if (r.allreduce(0, send_buf + (size_t)t * p.tile * p.d, output + (size_t)t * p.tile * p.d, (size_t)p.tile * p.d)) return 1;
+        if (r.allreduce(0, send_buf + (size_t)t * p.tile * r.row_bytes(), output + (size_t)t * p.tile * r.row_bytes(), (size_t)p.tile * p.d)) return 1;
     if (sync_stream(c, c->comm_streams[0], nullptr, 0)) return 1;
     return finish_timing(c, t0, st, false, false, r.launches);
 }
@@ -436,8 +465,10 @@ int run_stream_host_pipelined(efa_ctx* c, const uint16_t* Qh, const uint16_t* Kh
     if (scratch(c, p, p.S, p.S, p.num_tiles, p.S, (size_t)3 * nchunk + 2)) return 1;
     Run r{c, dev, p};
     __half* O_all = static_cast<__half*>(c->O_all);
-    __half* send_buf = static_cast<__half*>(c->send_buf);
-    __half* output = static_cast<__half*>(dev_out);
+    char* send_buf = static_cast<char*>(c->send_buf);
+    char* output = static_cast<char*>(dev_out);
+    char* host_bytes = reinterpret_cast<char*>(host_out);
+    const size_t rb = r.row_bytes();
     int* counters = c->counters;
     const int target = efa_blocks_per_tile(&p);
     auto ev_in = [&](int i) { return c->events[3 * i]; };
@@ -474,18 +505,18 @@ int run_stream_host_pipelined(efa_ctx* c, const uint16_t* Qh, const uint16_t* Kh
         for (int t = t0c; t < t0c + nt; t++)
             EFA_CU(api->cuStreamWaitValue32((CUstream)c->proj_stream, (CUdeviceptr)(counters + t), (cuuint32_t)target, CU_STREAM_WAIT_VALUE_GEQ));
         if (r.combine(O_all + (size_t)row0 * p.d_local, p.S, row0, rows, c->proj_stream)) return 1;
-        if (r.project(O_all + (size_t)row0 * p.d_local, send_buf + (size_t)row0 * p.d, rows)) return 1;
+        if (r.project(O_all + (size_t)row0 * p.d_local, send_buf + (size_t)row0 * rb, rows)) return 1;
         EFA_CUDA(cudaEventRecord(ev_proj(i), c->proj_stream));
         const int slot = i % c->ncomm;
         EFA_CUDA(cudaStreamWaitEvent(c->comm_streams[slot], ev_proj(i), 0));
         if (p.skip_comm) {
-            EFA_CUDA(cudaMemcpyAsync(output + (size_t)row0 * p.d, send_buf + (size_t)row0 * p.d, (size_t)rows * p.d * 2,
+            EFA_CUDA(cudaMemcpyAsync(output + (size_t)row0 * rb, send_buf + (size_t)row0 * rb, (size_t)rows * rb,
                                      cudaMemcpyDeviceToDevice, c->comm_streams[slot]));
-        } else if (r.allreduce(slot, send_buf + (size_t)row0 * p.d, output + (size_t)row0 * p.d, (size_t)rows * p.d)) return 1;
+        } else if (r.allreduce(slot, send_buf + (size_t)row0 * rb, output + (size_t)row0 * rb, (size_t)rows * p.d)) return 1;
         EFA_CUDA(cudaEventRecord(ev_ar(i), c->comm_streams[slot]));
         if (host_out) {
             EFA_CUDA(cudaStreamWaitEvent(c->d2h_stream, ev_ar(i), 0));
-            EFA_CUDA(cudaMemcpyAsync(host_out + (size_t)row0 * p.d, output + (size_t)row0 * p.d, (size_t)rows * p.d * 2,
+            EFA_CUDA(cudaMemcpyAsync(host_bytes + (size_t)row0 * rb, output + (size_t)row0 * rb, (size_t)rows * rb,
                                      cudaMemcpyDeviceToHost, c->d2h_stream));
         }
     }
@@ -510,8 +541,12 @@ int run_mode_impl(efa_ctx* c, int mode, const efa_weights& w, void* output, cons
         set_error("run_mode: mode %s writes no block output to add a residual to", kModeNames[mode]);
         return 2;
     }
+    if (p.proj_f32 && (residual || p.reduce == EFA_REDUCE_P2P)) {
+        set_error("run_mode: fp32 partial sums (proj_f32) go with the NCCL reduction and without a residual");
+        return 2;
+    }
     Run r{c, w, p};
-    __half* out = static_cast<__half*>(output);
+    char* out = static_cast<char*>(output);
     r.residual = static_cast<const __half*>(residual);
     r.out_base = out;
     switch (mode) {

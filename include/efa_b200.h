@@ -22,7 +22,7 @@
 extern "C" {
 #endif
 
-#define EFA_ABI_VERSION 1
+#define EFA_ABI_VERSION 2
 
 /* Element types of O / output buffers. */
 #define EFA_F32 0
@@ -148,6 +148,11 @@ typedef struct efa_params {
     int group_tiles;            /* stream mode, NCCL reduction: consecutive tiles handled by one projection +
                                    AllReduce launch (each tile's counter is still waited on). 1 = the reference's
                                    per-tile schedule; 0 = automatic (about S/8 rows per launch). */
+    int proj_f32;               /* 0 (default): the projection rounds its fp32 accumulator to fp16, the reduction sums
+                                   fp16 and `output` is fp16. 1: partial sums, reduction and `output` are fp32 — the
+                                   reference's types (attn_main.cu:262-273, run_drivers.cu:26-30), whose own --proj switch
+                                   chose fp32 or tf32 math (attn_bench.cu:55,113-117). Operands stay fp16 either way.
+                                   NCCL reduction only; not with a residual or the host-buffer entry point. */
     efa_flash_params flash_tc;
 } efa_params;
 
@@ -221,8 +226,8 @@ typedef struct efa_run_stats {
     int    kernel_launches;/* kernels of this library launched inside the timed region, this rank */
 } efa_run_stats;
 
-/* run_mode (run_drivers.cuh:22-26, run_drivers.cu:277-292). `output`: fp16 [S][d] device buffer,
- * the reduced result, identical on every rank (untouched by attn / attn_tiled). Collective. */
+/* run_mode (run_drivers.cuh:22-26, run_drivers.cu:277-292). `output`: fp16 [S][d] device buffer (fp32 when
+ * p->proj_f32), the reduced result, identical on every rank (untouched by attn / attn_tiled). Collective. */
 int efa_run_mode(efa_ctx* ctx, int mode, const efa_weights* w, void* output,
                  const efa_params* p, efa_run_stats* stats);
 

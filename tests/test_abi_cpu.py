@@ -25,7 +25,7 @@ def test_library_exports_every_declared_symbol(pkg):
 
 
 def test_abi_version(pkg):
-    assert pkg.lib().efa_abi_version() == 1
+    assert pkg.lib().efa_abi_version() == 2
 
 
 def test_mode_names_round_trip(pkg):

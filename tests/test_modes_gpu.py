@@ -207,3 +207,38 @@ def test_residual_is_rejected_where_no_block_output_exists(pkg, oracle, torch_cu
     p.skip_comm = 1
     with pytest.raises(pkg.EfaError, match="needs the projection and the reduction"):
         pkg.run_mode_residual(ctx, pkg.MODE_STREAM, w, res, out, p)
+
+
+@pytest.mark.parametrize("case", [(512, 256, 4, 128, 2, 1, 0), (1024, 512, 8, 128, 3, 2, 1), (2048, 1024, 8, 256, 2, 1, 1),
+                                  (2048, 4096, 32, 128, 2, 1, 1)],
+                         ids=lambda c: "S%d_d%d_H%d_t%d_n%d_s%d_c%d" % c)
+def test_fp32_partial_sums_and_output(pkg, oracle, torch_cuda, ctx, case):
+    """proj_f32: the projection keeps its fp32 accumulator, the reduction and the output are fp32 (the
+    reference's types, attn_main.cu:262-273, run_drivers.cu:26-30). Same gate as the fp16 path, and the
+    fp16 path's output must be this one rounded once (single rank: nothing is summed)."""
+    torch = torch_cuda
+    S, d, H, tile, nbuf, split, causal = case
+    p = pkg.make_params(S, d, H, tile, nbuf, split, causal)
+    # the wide shape runs the 256-column projection tile; it is checked on a sample of rows
+    bits, vals = ref_inputs_f16(oracle, S, d, H, 1, 0, 42) if d < 4096 else normal_inputs_f16(pkg, oracle, p, 0, 42)
+    rows = None if d < 4096 else np.arange(0, S, 7, dtype=np.int32)
+    ref = oracle.block_rows([vals], d, causal, rows)
+    dev = to_dev(torch, bits)
+    w = pkg.Weights(*(t.data_ptr() for t in dev))
+    for name in CHECKED_MODES:
+        half = torch.zeros((S, d), dtype=torch.float16, device="cuda")
+        p.proj_f32 = 0
+        pkg.run_mode(ctx, pkg.parse_mode(name), w, half, p)
+        out = torch.full((S, d), float("nan"), dtype=torch.float32, device="cuda")
+        p.proj_f32 = 1
+        pkg.kernel_status_reset()
+        st = pkg.run_mode(ctx, pkg.parse_mode(name), w, out, p)
+        torch.cuda.synchronize()
+        assert pkg.kernel_status()[0] == 0
+        assert st.kernel_launches > 0
+        got = out.cpu().numpy()
+        assert_close(oracle, got if rows is None else got[rows], ref, f"{name} fp32")
+        assert torch.equal(out.to(torch.float16), half), name
+    p.reduce = pkg.REDUCE_P2P
+    with pytest.raises(pkg.EfaError, match="NCCL reduction"):
+        pkg.run_mode(ctx, pkg.MODE_STREAM, w, out, p)

@@ -45,12 +45,14 @@ WORKER = textwrap.dedent("""
         ref = oracle.block_rows(per_rank, d, causal)
         dev = [torch.from_numpy(b.view(np.float16)).cuda() for b in mine]
         w = pkg.Weights(*(t.data_ptr() for t in dev))
-        for reduce in reduces:
+        for reduce in reduces:             # 0: NCCL, fp16 partial sums; 1: fused peer-memory kernel; 2: NCCL, fp32 partial sums
             if reduce == 1 and (split != 1 or d % (128 * world) != 0):
                 continue
-            p.reduce = reduce
-            for name in (("megatron", "sync", "overlap", "stream") if reduce == 0 else ("stream",)):
-                out = outs.setdefault((S, d), torch.empty((S, d), dtype=torch.float16, device="cuda"))
+            p.reduce = 1 if reduce == 1 else 0
+            p.proj_f32 = 1 if reduce == 2 else 0
+            odt = torch.float32 if reduce == 2 else torch.float16
+            for name in (("megatron", "sync", "overlap", "stream") if reduce != 1 else ("stream",)):
+                out = outs.setdefault((S, d, odt), torch.empty((S, d), dtype=odt, device="cuda"))
                 out.fill_(float("nan"))
                 torch.cuda.synchronize()
                 dist.barrier()
@@ -94,7 +96,7 @@ def run_workers(tmp_path, nproc, reduces):
 
 
 def test_two_ranks_nccl_reduction(tmp_path):
-    run_workers(tmp_path, 2, (0,))
+    run_workers(tmp_path, 2, (0, 2))
 
 
 def test_two_ranks_fused_p2p_reduction(tmp_path):
@@ -103,4 +105,4 @@ def test_two_ranks_fused_p2p_reduction(tmp_path):
 
 
 def test_eight_ranks_both_reductions(tmp_path):
-    run_workers(tmp_path, 8, (0, 1))
+    run_workers(tmp_path, 8, (0, 1, 2))
