@@ -1,7 +1,8 @@
 // Execution modes of the tensor-parallel attention block (attention -> projection -> sum AllReduce).
 // Counterpart of run_drivers.cu of eager-flash-attention (run_drivers.cu:9-30, 48-292): same seven
 // modes, same timing convention (barrier, host clock, enqueue, synchronise, max over ranks), same
-// stream roles; fp16 O / projection / reduction instead of fp32, and scratch cached in the context.
+// stream roles; fp16 O, and fp16 (or, with proj_f32, the reference's fp32) partial sums / reduction / output;
+// scratch cached in the context.
 #include "runtime.h"
 
 #include "fa_fwd_sm100.cuh"
