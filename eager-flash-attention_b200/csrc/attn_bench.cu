@@ -23,9 +23,10 @@ static int g_rank = 0;
 
 static const char* arg_str(int argc, char** argv, const char* flag, const char* def)
 {
+    const char* val = def;                       // the last occurrence wins, so a wrapper's defaults can be overridden
     for (int i = 1; i + 1 < argc; i++)
-        if (std::strcmp(argv[i], flag) == 0) return argv[i + 1];
-    return def;
+        if (std::strcmp(argv[i], flag) == 0) val = argv[i + 1];
+    return val;
 }
 static int arg_int(int argc, char** argv, const char* flag, int def)
 {

@@ -6,6 +6,12 @@
 Suites follow bench_sweep.py:73-123 of eager-flash-attention (core, kernel, modes, scaling, model,
 causal, comm), with srun replaced by efa_launch and the legacy kernel dropped. Tile sizes include the
 small tiles of the B200 plan (64/128/256) next to the reference's S/16 and S/8.
+
+The `overlap` suite is a diagnosis of exposed communication at the scaling shape: stream mode with and
+without the collectives, over the knobs that decide how projection and AllReduce launches find SMs while
+the attention kernel runs (tiles per launch, split-KV item length, reserved SMs, NCCL's CTA budget), plus
+one traced run whose per-group timeline goes to stderr. Its runs differ in flags and environment that
+the CSV columns do not show, so each CSV row of that suite is preceded by a `# ...` line naming them.
 """
 import argparse
 import os
@@ -48,9 +54,26 @@ def suite_commands(name, ranks):
             for ncomm in (1, 2, 4, 8):
                 for causal in ((), ("--causal",)):
                     cmds.append(["--S", 65536, "--tile", tile, "--ncomm", ncomm, *causal, "--modes", "megatron,stream"])
+    elif name == "overlap":
+        base = ["--S", 32768, "--H", 32, "--d_h", 128, "--causal", "--tile", 128, "--ncomm", 4]
+        cmds.append((base + ["--modes", "attn,megatron,stream"], {}))
+        cmds.append((base + ["--modes", "stream", "--no_comm"], {}))
+        cmds.append((base + ["--modes", "stream", "--trials", 1, "--warmup", 1], {"EFA_TRACE": "1"}))
+        for gt in (16, 64, 128):
+            cmds.append((base + ["--modes", "stream", "--group_tiles", gt], {}))
+        for split in (2, 4):
+            cmds.append((base + ["--modes", "stream", "--split", split], {}))
+        for ctas in (4, 8, 16):
+            cmds.append((base + ["--modes", "stream"], {"NCCL_MAX_CTAS": str(ctas)}))
+            cmds.append((base + ["--modes", "stream"], {"NCCL_MAX_CTAS": str(ctas), "EFA_RESERVE_SMS": str(2 * ctas)}))
+        cmds.append((base + ["--modes", "stream", "--reduce", "p2p"], {}))
     else:
         raise ValueError(f"unknown suite {name!r}")
-    return [[str(x) for x in c] for c in cmds]
+    out = []
+    for c in cmds:
+        args, env = c if isinstance(c, tuple) else (c, {})
+        out.append(([str(x) for x in args], env))
+    return out
 
 
 def main(argv=None):
@@ -71,13 +94,21 @@ def main(argv=None):
         print(HEADER, file=out, flush=True)
     rc = 0
     for suite in args.suite.split(","):
-        for cmd in suite_commands(suite.strip(), args.ranks):
-            full = [args.launcher, "-n", str(args.ranks), args.bench, *cmd, "--warmup", str(args.warmup),
-                    "--trials", str(args.trials), "--no-header", *args.extra.split()]
+        for cmd, env in suite_commands(suite.strip(), args.ranks):
+            # flags of the suite come last, so a suite may override --warmup / --trials
+            full = [args.launcher, "-n", str(args.ranks), args.bench, "--warmup", str(args.warmup),
+                    "--trials", str(args.trials), "--no-header", *args.extra.split(), *cmd]
+            label = " ".join(f"{k}={v}" for k, v in env.items())
             if args.dry_run:
-                print(" ".join(full))
+                print((label + " " if label else "") + " ".join(full))
                 continue
-            r = subprocess.run(full, capture_output=True, text=True)
+            if env:
+                print(f"# {label} {' '.join(cmd)}", file=out, flush=True)
+            elif suite.strip() == "overlap":
+                print(f"# {' '.join(cmd)}", file=out, flush=True)
+            r = subprocess.run(full, capture_output=True, text=True, env=dict(os.environ, **env))
+            if "EFA_TRACE" in env:
+                sys.stderr.write(r.stderr)
             if r.returncode != 0:
                 print(f"# FAILED ({r.returncode}): {' '.join(full)}\n# {r.stderr.strip()[-300:]}", file=sys.stderr)
                 rc = 1

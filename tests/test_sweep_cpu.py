@@ -58,3 +58,13 @@ def test_sweep_dry_run_lists_the_reference_suites():
     assert len(lines) > 40
     assert all("efa_launch -n 8" in l for l in lines)
     assert any("--modes comm" in l for l in lines) and any("--causal" in l for l in lines)
+
+
+def test_overlap_suite_names_its_environment():
+    r = subprocess.run([sys.executable, os.path.join(SWEEP, "bench_sweep.py"), "--ranks", "8", "--suite", "overlap", "--dry-run"],
+                       capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    lines = [l for l in r.stdout.splitlines() if "attn_bench" in l]
+    assert any(l.startswith("EFA_TRACE=1 ") for l in lines)
+    assert any(l.startswith("NCCL_MAX_CTAS=8 EFA_RESERVE_SMS=16 ") for l in lines)
+    assert any("--no_comm" in l for l in lines) and any("--split 4" in l for l in lines) and any("--reduce p2p" in l for l in lines)
