@@ -36,3 +36,21 @@ def test_reference_test_program_passes_with_this_librarys_kernels(torch_cuda):
         elif kernel == "tc" and line.rstrip().endswith("PASS"):
             tc_lines += 1
     assert tc_lines == 13 * 3 * 4, tc_lines
+
+
+EXE_DRIVERS = os.path.join(ROOT, "oracle", "_ref", "attn_tests_dropin_drivers")
+
+
+@pytest.mark.skipif(os.environ.get("EFA_TEST_DROPIN_DRIVERS") != "1",
+                    reason="set EFA_TEST_DROPIN_DRIVERS=1: the run_drivers-level drop-in has run the reference's benchmark "
+                           "program on a B200 but not yet its test program")
+def test_reference_test_program_passes_with_this_librarys_run_modes(torch_cuda):
+    """Both translation units exchanged (make -C oracle dropin_drivers): every tensor-core configuration of the
+    reference's run_mode goes through efa_run_mode with fp32 partial sums and output."""
+    if not os.path.exists(EXE_DRIVERS):
+        pytest.skip("oracle/_ref/attn_tests_dropin_drivers is not built")
+    r = subprocess.run([EXE_DRIVERS], capture_output=True, text=True, timeout=600)
+    tail = r.stdout[-3000:] + r.stderr[-2000:]
+    assert r.returncode == 0, tail
+    m = re.search(r"(\d+) passed, (\d+) failed, (\d+) skipped", r.stdout)
+    assert m and int(m.group(2)) == 0, tail
