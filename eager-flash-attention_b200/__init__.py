@@ -25,7 +25,8 @@ LIB_PATH = os.path.join(_HERE, "libefa_b200.so")
 F32, F16 = 0, 1
 MODE_ATTN, MODE_ATTN_TILED, MODE_MEGATRON, MODE_SYNC, MODE_OVERLAP, MODE_STREAM, MODE_COMM = range(7)
 MODE_NAMES = ("attn", "attn_tiled", "megatron", "sync", "overlap", "stream", "comm")
-REDUCE_NCCL, REDUCE_P2P = 0, 1
+REDUCE_NCCL, REDUCE_P2P, REDUCE_NVLS = 0, 1, 2
+ROWS_AUTO, ROWS_ASCENDING, ROWS_DESCENDING = 0, 1, 2
 RECIPE_REF, RECIPE_NORMAL = 0, 1
 
 
@@ -51,7 +52,8 @@ class Params(C.Structure):
                 ("tile", C.c_int), ("num_tiles", C.c_int),
                 ("nbuf", C.c_int), ("split", C.c_int), ("causal", C.c_int),
                 ("skip_proj", C.c_int), ("skip_comm", C.c_int), ("reduce", C.c_int), ("group_tiles", C.c_int),
-                ("proj_f32", C.c_int), ("flash_tc", FlashParams)]
+                ("proj_f32", C.c_int), ("row_order", C.c_int), ("reduce_ctas", C.c_int), ("band_rows", C.c_int),
+                ("reserve_sms", C.c_int), ("trace", C.c_int), ("flash_tc", FlashParams)]
 
 
 _BARRIER_FN = C.CFUNCTYPE(C.c_int, C.c_void_p)
@@ -103,7 +105,8 @@ _SIGNATURES = {
     "efa_make_params": (C.c_int, [C.POINTER(Params), C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     "efa_attn_check_params": (C.c_char_p, [C.POINTER(Params)]),
     "efa_blocks_per_tile": (C.c_int, [C.POINTER(Params)]),
-    "efa_stream_plan": (C.c_int, [C.POINTER(Params), C.POINTER(StreamGroup), C.c_int, C.POINTER(C.c_int)]),
+    "efa_stream_plan": (C.c_int, [C.POINTER(Params), C.POINTER(StreamGroup), C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "efa_ctx_set_wait_limit_ms": (C.c_int, [C.c_void_p, C.c_double, C.c_double]),
     "efa_world_selftest": (C.c_int, [C.POINTER(WorldStruct)]),
     "efa_make_ctx": (C.c_int, [C.POINTER(C.c_void_p), C.POINTER(WorldStruct), C.c_int, C.c_int]),
     "efa_destroy_ctx": (C.c_int, [C.c_void_p]),
@@ -194,13 +197,14 @@ def blocks_per_tile(p: Params) -> int:
 
 
 def stream_plan(p: Params):
-    """Launch plan of stream mode (NCCL reduction): ([(first_tile, ntiles), ...], band_rows). Host arithmetic."""
+    """Launch plan of stream mode: ([(first_tile, ntiles), ...] in the order the groups are waited for, band_rows,
+    descending). Host arithmetic."""
     groups = (StreamGroup * max(1, p.num_tiles))()
-    band = C.c_int(0)
-    n = lib().efa_stream_plan(C.byref(p), groups, p.num_tiles, C.byref(band))
+    band, desc = C.c_int(0), C.c_int(0)
+    n = lib().efa_stream_plan(C.byref(p), groups, p.num_tiles, C.byref(band), C.byref(desc))
     if n < 0:
         raise EfaError(f"stream_plan failed: {last_error()}")
-    return [(groups[i].first_tile, groups[i].ntiles) for i in range(n)], band.value
+    return [(groups[i].first_tile, groups[i].ntiles) for i in range(n)], band.value, bool(desc.value)
 
 
 def mode_name(mode: int) -> str:
@@ -366,6 +370,12 @@ class Ctx:
 
 def make_ctx(world: World, ncomm: int = 1, prioritize: bool = True) -> Ctx:
     return Ctx(world, ncomm, prioritize)
+
+
+def set_wait_limit_ms(ctx: Ctx, device_ms: float = 0.0, host_ms: float = 0.0) -> None:
+    """Limits of the guarded waits: how long a kernel polls a counter or flag that never comes before it reports
+    a status, and how long run_mode waits for a stream before it releases pending counter waits (<= 0: unchanged)."""
+    _check(lib().efa_ctx_set_wait_limit_ms(ctx.handle, float(device_ms), float(host_ms)), "set_wait_limit_ms")
 
 
 def destroy_ctx(ctx: Ctx) -> None:

@@ -13,7 +13,8 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
-#include <numeric>
+#include <initializer_list>
+#include <utility>
 #include <string>
 #include <vector>
 
@@ -21,24 +22,35 @@
 
 static int g_rank = 0;
 
-static const char* arg_str(int argc, char** argv, const char* flag, const char* def)
-{
-    const char* val = def;                       // the last occurrence wins, so a wrapper's defaults can be overridden
-    for (int i = 1; i + 1 < argc; i++)
-        if (std::strcmp(argv[i], flag) == 0) val = argv[i + 1];
-    return val;
-}
-static int arg_int(int argc, char** argv, const char* flag, int def)
-{
-    const char* s = arg_str(argc, argv, flag, nullptr);
-    return s ? std::atoi(s) : def;
-}
-static bool has_flag(int argc, char** argv, const char* flag)
-{
-    for (int i = 1; i < argc; i++)
-        if (std::strcmp(argv[i], flag) == 0) return true;
-    return false;
-}
+// Command line as a table: "--name value" pairs and bare "--switch" words. A name given twice keeps its last
+// value, so a wrapper's defaults can be overridden by appending.
+class CommandLine {
+public:
+    CommandLine(int argc, char** argv, std::initializer_list<const char*> switches)
+    {
+        for (int i = 1; i < argc; i++) {
+            const std::string word = argv[i];
+            const bool is_switch = std::find_if(switches.begin(), switches.end(), [&](const char* s) { return word == s; }) != switches.end();
+            if (is_switch) { flags_.push_back(word); continue; }
+            if (word.rfind("--", 0) == 0 && i + 1 < argc) { values_.emplace_back(word, argv[i + 1]); i++; }
+        }
+    }
+    bool on(const char* name) const { return std::find(flags_.begin(), flags_.end(), name) != flags_.end(); }
+    std::string text(const char* name, const char* fallback) const
+    {
+        std::string v = fallback;
+        for (const auto& kv : values_) if (kv.first == name) v = kv.second;
+        return v;
+    }
+    int number(const char* name, int fallback) const
+    {
+        const std::string v = text(name, "");
+        return v.empty() ? fallback : std::atoi(v.c_str());
+    }
+private:
+    std::vector<std::pair<std::string, std::string>> values_;
+    std::vector<std::string> flags_;
+};
 
 [[noreturn]] static void fail(const char* what)
 {
@@ -63,14 +75,18 @@ static int cb_gather(void*, const void* in, void* out, size_t n)
     return MPI_Allgather(in, (int)n, MPI_BYTE, out, (int)n, MPI_BYTE, MPI_COMM_WORLD) != MPI_SUCCESS;
 }
 
-struct Stats { double min, max, mean, median, std; };
-static Stats compute_stats(std::vector<double> v)
+// The five figures of a CSV row (attn_bench.cu:149-152 of the reference prints the same five).
+struct Summary { double lo, hi, mean, median, stddev; };
+static Summary summarize(const std::vector<double>& samples)
 {
-    std::sort(v.begin(), v.end());
-    const double mean = std::accumulate(v.begin(), v.end(), 0.0) / v.size();
-    double sq = 0.0;
-    for (double x : v) sq += (x - mean) * (x - mean);
-    return {v.front(), v.back(), mean, v[v.size() / 2], std::sqrt(sq / v.size())};
+    Summary r{samples[0], samples[0], 0.0, 0.0, 0.0};
+    for (double x : samples) { r.lo = std::min(r.lo, x); r.hi = std::max(r.hi, x); r.mean += x / samples.size(); }
+    for (double x : samples) r.stddev += (x - r.mean) * (x - r.mean) / samples.size();
+    r.stddev = std::sqrt(r.stddev);
+    std::vector<double> mid(samples);
+    std::nth_element(mid.begin(), mid.begin() + mid.size() / 2, mid.end());
+    r.median = mid[mid.size() / 2];                       // upper median for an even count, as the reference takes it
+    return r;
 }
 
 static void usage(const char* prog)
@@ -80,7 +96,8 @@ static void usage(const char* prog)
         "          [--nbuf 2] [--split 1] [--ncomm 1] [--warmup 3] [--trials 10]\n"
         "          [--modes attn,attn_tiled,megatron,sync,overlap,stream,comm] [--no-header]\n"
         "          [--causal] [--proj fp16|fp32] [--no_prio] [--no_proj] [--no_comm]\n"
-        "          [--reduce nccl|p2p] [--group_tiles 0] [--data normal|ref] [--seed 42] [--residual]\n", prog);
+        "          [--reduce nccl|p2p|nvls] [--group_tiles 0] [--order auto|asc|desc] [--data normal|ref] [--seed 42] [--residual]\n"
+        "          [--band_rows 0] [--reserve_sms 0] [--reduce_ctas 0] [--trace]\n", prog);
 }
 
 int main(int argc, char** argv)
@@ -95,22 +112,25 @@ int main(int argc, char** argv)
     const int device = g_rank % ndev;
     CUDA_OK(cudaSetDevice(device));
 
-    if (has_flag(argc, argv, "--help")) {
+    const CommandLine cl(argc, argv, {"--help", "--causal", "--no-header", "--no_prio", "--no_proj", "--no_comm", "--residual", "--trace"});
+    if (cl.on("--help")) {
         if (g_rank == 0) usage(argv[0]);
         MPI_Finalize();
         return 0;
     }
-    const int S = arg_int(argc, argv, "--S", 4096), H = arg_int(argc, argv, "--H", 16), d_h = arg_int(argc, argv, "--d_h", 64);
-    const int tile = arg_int(argc, argv, "--tile", 256), nbuf = arg_int(argc, argv, "--nbuf", 2);
-    const int split = arg_int(argc, argv, "--split", 1), ncomm = arg_int(argc, argv, "--ncomm", 1);
-    const int causal = has_flag(argc, argv, "--causal") ? 1 : 0;
-    const int warmup = arg_int(argc, argv, "--warmup", 3), trials = arg_int(argc, argv, "--trials", 10);
-    const int seed = arg_int(argc, argv, "--seed", 42);
-    const char* kernel = arg_str(argc, argv, "--kernel", "tc");
-    const char* proj = arg_str(argc, argv, "--proj", "fp16");
-    const char* reduce = arg_str(argc, argv, "--reduce", "nccl");
-    const char* data = arg_str(argc, argv, "--data", "normal");
-    const bool header = !has_flag(argc, argv, "--no-header");
+    const int S = cl.number("--S", 4096), H = cl.number("--H", 16), d_h = cl.number("--d_h", 64);
+    const int tile = cl.number("--tile", 256), nbuf = cl.number("--nbuf", 2);
+    const int split = cl.number("--split", 1), ncomm = cl.number("--ncomm", 1);
+    const int causal = cl.on("--causal") ? 1 : 0;
+    const int warmup = cl.number("--warmup", 3), trials = cl.number("--trials", 10);
+    const int seed = cl.number("--seed", 42);
+    const std::string kernel_s = cl.text("--kernel", "tc"), proj_s = cl.text("--proj", "fp16");
+    const std::string reduce_s = cl.text("--reduce", "nccl"), data_s = cl.text("--data", "normal"), order_s = cl.text("--order", "auto");
+    const char* kernel = kernel_s.c_str();
+    const char* proj = proj_s.c_str();
+    const char* reduce = reduce_s.c_str();
+    const char* data = data_s.c_str();
+    const bool header = !cl.on("--no-header");
     const int d = H * d_h;
 
     if (std::strcmp(kernel, "tc") != 0) fail("--kernel must be tc (the scalar v1 prototype is not part of this build)");
@@ -127,29 +147,35 @@ int main(int argc, char** argv)
 
     std::vector<int> modes;
     {
-        std::string list = arg_str(argc, argv, "--modes", "attn,megatron,sync,overlap,stream");
-        size_t start = 0;
-        while (start <= list.size()) {
-            size_t end = list.find(',', start);
-            if (end == std::string::npos) end = list.size();
-            const std::string tok = list.substr(start, end - start);
-            if (!tok.empty()) {
-                const int m = efa_parse_mode(tok.c_str());
-                if (m < 0) { if (g_rank == 0) fprintf(stderr, "ERROR: unknown mode '%s'\n", tok.c_str()); MPI_Abort(MPI_COMM_WORLD, 1); }
-                modes.push_back(m);
-            }
-            start = end + 1;
+        // comma-separated mode names; empty items are ignored
+        std::string item;
+        const std::string list = cl.text("--modes", "attn,megatron,sync,overlap,stream") + ",";
+        for (char ch : list) {
+            if (ch != ',') { item.push_back(ch); continue; }
+            if (item.empty()) continue;
+            const int m = efa_parse_mode(item.c_str());
+            if (m < 0) { if (g_rank == 0) fprintf(stderr, "ERROR: unknown mode '%s'\n", item.c_str()); MPI_Abort(MPI_COMM_WORLD, 1); }
+            modes.push_back(m);
+            item.clear();
         }
     }
 
     efa_params p;
     EFA_OK(efa_make_params(&p, S, d, H, tile, nbuf, split, causal, world));
-    p.skip_proj = has_flag(argc, argv, "--no_proj");
-    p.skip_comm = has_flag(argc, argv, "--no_comm");
-    p.group_tiles = arg_int(argc, argv, "--group_tiles", 0);
+    p.skip_proj = cl.on("--no_proj");
+    p.skip_comm = cl.on("--no_comm");
+    p.group_tiles = cl.number("--group_tiles", 0);
+    p.band_rows = cl.number("--band_rows", 0);
+    p.reserve_sms = cl.number("--reserve_sms", 0);
+    p.reduce_ctas = cl.number("--reduce_ctas", 0);
+    p.trace = cl.on("--trace") ? 1 : 0;
     p.proj_f32 = proj_f32;
     if (std::strcmp(reduce, "p2p") == 0) p.reduce = EFA_REDUCE_P2P;
-    else if (std::strcmp(reduce, "nccl") != 0) fail("--reduce must be nccl or p2p");
+    else if (std::strcmp(reduce, "nvls") == 0) p.reduce = EFA_REDUCE_NVLS;
+    else if (std::strcmp(reduce, "nccl") != 0) fail("--reduce must be nccl, p2p or nvls");
+    if (order_s == "asc") p.row_order = EFA_ROWS_ASCENDING;
+    else if (order_s == "desc") p.row_order = EFA_ROWS_DESCENDING;
+    else if (order_s != "auto") fail("--order must be auto, asc or desc");
     if (const char* why = efa_attn_check_params(&p)) {
         if (g_rank == 0) fprintf(stderr, "ERROR: invalid params: %s\n", why);
         MPI_Abort(MPI_COMM_WORLD, 1);
@@ -163,7 +189,7 @@ int main(int argc, char** argv)
     w.rank = g_rank; w.size = world; w.local_device = device;
     w.barrier = cb_barrier; w.allreduce_max_f64 = cb_max; w.bcast_bytes = cb_bcast; w.allgather_bytes = cb_gather;
     efa_ctx* ctx = nullptr;
-    EFA_OK(efa_make_ctx(&ctx, &w, ncomm, !has_flag(argc, argv, "--no_prio")));
+    EFA_OK(efa_make_ctx(&ctx, &w, ncomm, !cl.on("--no_prio")));
 
     const size_t qkv_n = (size_t)p.H_local * p.S * p.d_h, wo_n = (size_t)p.d_local * p.d, out_n = (size_t)p.S * p.d;
     std::vector<uint16_t> hq(qkv_n), hk(qkv_n), hv(qkv_n), hw(wo_n);
@@ -180,7 +206,7 @@ int main(int argc, char** argv)
     // --residual: time the block together with the step after it (output = residual + block, the residual
     // added to each reduced group of rows as it lands); modes without a block output run as usual.
     void* residual = nullptr;
-    if (has_flag(argc, argv, "--residual")) {
+    if (cl.on("--residual")) {
         if (proj_f32) fail("--residual goes with --proj fp16");
         CUDA_OK(cudaMalloc(&residual, out_n * 2));
         CUDA_OK(cudaMemset(residual, 0x2c, out_n * 2));          // every element 0x2c2c = 0.0652
@@ -205,11 +231,11 @@ int main(int argc, char** argv)
             MPI_Abort(MPI_COMM_WORLD, 1);
         }
         if (g_rank == 0) {
-            const Stats s = compute_stats(times);
-            const Stats a = compute_stats(attn);
+            const Summary s = summarize(times);
+            const Summary a = summarize(attn);
             printf("%d,%d,%d,%d,%d,%s,%d,%d,%d,%d,%s,%s,%.4f,%.4f,%.4f,%.4f,%.4f,%.1f,%.4f,%s,%s\n",
                    S, H, d_h, causal, world, kernel, tile, nbuf, split, ncomm, proj, efa_mode_name(mode),
-                   s.min, s.max, s.mean, s.median, s.std, (double)S / (s.median * 1e-3), a.median, reduce, data);
+                   s.lo, s.hi, s.mean, s.median, s.stddev, (double)S / (s.median * 1e-3), a.median, reduce, data);
             fflush(stdout);
         }
     }

@@ -112,7 +112,15 @@ extern "C" int efa_run_mode_host(efa_ctx* c, int mode,
     const size_t ob = (size_t)p->S * p->d * 2;
     {
         size_t a = c->h_qkv_bytes, b = c->h_qkv_bytes, d = c->h_qkv_bytes;
+        const bool fresh = a < qkv || !c->h_Q || !c->h_K || !c->h_V;
         if (ensure_bytes(&c->h_Q, &a, qkv) || ensure_bytes(&c->h_K, &b, qkv) || ensure_bytes(&c->h_V, &d, qkv)) return 1;
+        if (fresh) {
+            // Rows that a chunked copy has not delivered yet may still be touched by a tile load (their scores are
+            // masked, but 0 * NaN is NaN): new staging starts as zeros, never as whatever the allocator returned.
+            EFA_CUDA(cudaMemset(c->h_Q, 0, a));
+            EFA_CUDA(cudaMemset(c->h_K, 0, b));
+            EFA_CUDA(cudaMemset(c->h_V, 0, d));
+        }
         c->h_qkv_bytes = a < b ? (a < d ? a : d) : (b < d ? b : d);
         if (ensure_bytes(&c->h_W, &c->h_w_bytes, wb) || ensure_bytes(&c->h_out, &c->h_out_bytes, ob)) return 1;
     }

@@ -33,6 +33,8 @@ __device__ __forceinline__ float ex2(float x)
 
 // Warp-specialised two-tile kernel (fa_fwd_ws_sm100.cu), d_h = 64 or 128.
 // reserve_sms > 0: persistent grid that leaves that many SMs without an attention CTA.
+// K and V maps for it have boxes of fa_ws_kv_box_rows() rows (its stage length); Q maps 128 rows.
+int fa_ws_kv_box_rows();
 int fa_forward_ws(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FaArgs& a,
                   int d_h, bool out_f16, int reserve_sms, cudaStream_t stream);
 

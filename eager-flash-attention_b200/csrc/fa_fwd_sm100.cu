@@ -332,38 +332,63 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ,
     if (warp == 0) tmem_dealloc(tmem_base, C::TMEM_COLS);
 }
 
-// One thread per (row, column pair): O = sum_i 2^(m_i - M) O_i / sum_i 2^(m_i - M) l_i
-template <bool OUT_F16>
-__global__ void combine_splits_kernel(const float* __restrict__ O_part, const float* __restrict__ m_part,
-                                      const float* __restrict__ l_part, void* __restrict__ O,
-                                      int row0, int rows, int ws_rows, int d_local, int H_local, int d_h, int split)
-{
-    const int pairs = d_local / 2;
-    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= (long)rows * pairs) return;
-    const int r = (int)(idx / pairs);
-    const int col = (int)(idx % pairs) * 2;
-    const int head = col / d_h;
-    const size_t row = (size_t)row0 + r;
+// Merge of the split-KV partials (the job of combine_kernel, flash_attn_tc.cu:319-349):
+//     O = sum_i w_i O_i / sum_i w_i l_i,   w_i = 2^(m_i - max_k m_k).
+// A block takes CB_ROWS rows. First the normalised weights w_i / sum_k w_k l_k are computed once per (row, head)
+// into shared memory; then every thread merges 16-byte column chunks with them, so the row maxima and
+// denominators are read and exponentiated once per head and row, not once per output element. HBM-bound:
+// (split + 1/2 or 1) * rows * d_local * 4 bytes.
+constexpr int CB_ROWS = 8;
 
-    float M = -INFINITY;
-    for (int i = 0; i < split; i++)
-        M = fmaxf(M, m_part[((size_t)i * ws_rows + row) * H_local + head]);
-    float L = 0.f, ax = 0.f, ay = 0.f;
-    for (int i = 0; i < split; i++) {
-        const size_t s = ((size_t)i * ws_rows + row) * H_local + head;
-        const float w = exp2f(m_part[s] - M);
-        L += w * l_part[s];
-        const float2 v = *reinterpret_cast<const float2*>(O_part + ((size_t)i * ws_rows + row) * d_local + col);
-        ax += w * v.x;
-        ay += w * v.y;
+template <bool OUT_F16>
+__global__ void __launch_bounds__(256)
+combine_splits_kernel(const float* __restrict__ O_part, const float* __restrict__ m_part,
+                      const float* __restrict__ l_part, void* __restrict__ O,
+                      int row0, int rows, int ws_rows, int d_local, int H_local, int d_h, int split)
+{
+    extern __shared__ float weight[];                       // [CB_ROWS][H_local][split]
+    const int first = blockIdx.x * CB_ROWS;
+    const int nrows = min(CB_ROWS, rows - first);
+
+    for (int e = threadIdx.x; e < nrows * H_local; e += blockDim.x) {
+        const int rr = e / H_local, head = e - rr * H_local;
+        const size_t base = (size_t)(row0 + first + rr) * H_local + head;
+        const size_t step = (size_t)ws_rows * H_local;      // distance between splits
+        float top = -INFINITY;
+        for (int i = 0; i < split; i++) top = fmaxf(top, m_part[base + i * step]);
+        float denom = 0.f;
+        float* w = weight + (size_t)e * split;
+        for (int i = 0; i < split; i++) {
+            w[i] = exp2f(m_part[base + i * step] - top);
+            denom += w[i] * l_part[base + i * step];
+        }
+        const float inv = 1.f / denom;
+        for (int i = 0; i < split; i++) w[i] *= inv;
     }
-    const float inv = 1.f / L;
-    if constexpr (OUT_F16) {
-        *reinterpret_cast<__half2*>(reinterpret_cast<__half*>(O) + (size_t)r * d_local + col) =
-            __floats2half2_rn(ax * inv, ay * inv);
-    } else {
-        *reinterpret_cast<float2*>(reinterpret_cast<float*>(O) + (size_t)r * d_local + col) = make_float2(ax * inv, ay * inv);
+    __syncthreads();
+
+    const int chunks = d_local / 4;                         // float4 chunks per row (d_h is a multiple of 16)
+    for (int e = threadIdx.x; e < nrows * chunks; e += blockDim.x) {
+        const int rr = e / chunks, c = e - rr * chunks;
+        const int head = (c * 4) / d_h;
+        const float* w = weight + ((size_t)rr * H_local + head) * split;
+        const float4* src = reinterpret_cast<const float4*>(O_part + (size_t)(row0 + first + rr) * d_local) + c;
+        const size_t step4 = (size_t)ws_rows * d_local / 4;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int i = 0; i < split; i++) {
+            const float4 v = __ldg(src + i * step4);
+            acc.x = fmaf(w[i], v.x, acc.x); acc.y = fmaf(w[i], v.y, acc.y);
+            acc.z = fmaf(w[i], v.z, acc.z); acc.w = fmaf(w[i], v.w, acc.w);
+        }
+        const size_t out = (size_t)(first + rr) * d_local + (size_t)c * 4;
+        if constexpr (OUT_F16) {
+            uint2 packed;
+            packed.x = pack_f16x2(acc.x, acc.y);
+            packed.y = pack_f16x2(acc.z, acc.w);
+            *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(O) + out) = packed;
+        } else {
+            *reinterpret_cast<float4*>(reinterpret_cast<float*>(O) + out) = acc;
+        }
     }
 }
 
@@ -376,22 +401,24 @@ __global__ void f32_to_f16_kernel(const float* __restrict__ in, __half* __restri
 
 // Tensor maps depend only on (pointer, S, H_local, d_h); drivers launch the same tensors over and over.
 struct TmapKey {
-    const void* ptr; int S, H, D;
-    bool operator<(const TmapKey& o) const { return std::tie(ptr, S, H, D) < std::tie(o.ptr, o.S, o.H, o.D); }
+    const void* ptr; int S, H, D, rows;
+    bool operator<(const TmapKey& o) const { return std::tie(ptr, S, H, D, rows) < std::tie(o.ptr, o.S, o.H, o.D, o.rows); }
 };
 
-int get_qkv_tmap(const void* ptr, int S, int H_local, int D, CUtensorMap* out)
+// box_rows: rows of the tensor per TMA box (128 for Q tiles and for the one-tile kernel's K/V stages, the
+// two-tile kernel's stage length for its K and V).
+int get_qkv_tmap(const void* ptr, int S, int H_local, int D, int box_rows, CUtensorMap* out)
 {
     static std::map<TmapKey, CUtensorMap> cache;
     static std::mutex mu;
     std::lock_guard<std::mutex> lock(mu);
-    TmapKey key{ptr, S, H_local, D};
+    TmapKey key{ptr, S, H_local, D, box_rows};
     auto it = cache.find(key);
     if (it != cache.end()) { *out = it->second; return 0; }
     const int boxc = D >= 64 ? 64 : D;
     unsigned long long dims[3] = {(unsigned long long)D, (unsigned long long)S, (unsigned long long)H_local};
     unsigned long long strides[2] = {(unsigned long long)D * 2ull, (unsigned long long)S * D * 2ull};
-    unsigned box[3] = {(unsigned)boxc, 128u, 1u};
+    unsigned box[3] = {(unsigned)boxc, (unsigned)box_rows, 1u};
     CUtensorMap tm;
     if (make_tmap_f16(&tm, ptr, 3, dims, strides, box)) return 1;
     if (cache.size() > 256) cache.clear();
@@ -433,7 +460,7 @@ const char* fa_check_params(const efa_flash_params& p, int q_rows)
 int fa_forward(const void* Q, const void* K, const void* V, void* O, int o_dtype,
                const efa_flash_partials* part, int q_start, int q_rows,
                const efa_flash_params& p, cudaStream_t stream, int* tile_counters, int tile_rows, int reserve_sms,
-               int band_rows)
+               int band_rows, int heavy_first)
 {
     if (const char* why = fa_check_params(p, q_rows)) { set_error("flash_attn_tc_forward: %s", why); return 2; }
     if (q_start < 0 || q_start % 64 != 0 || q_start + q_rows > p.S) {
@@ -455,9 +482,12 @@ int fa_forward(const void* Q, const void* K, const void* V, void* O, int o_dtype
         return 2;
     }
 
+    // d_h = 64 / 128 run on the warp-specialised two-tile kernel, 16 / 32 on the one-tile kernel below.
+    const bool two_tile = (p.d_h == 64 || p.d_h == 128);
+    const int kv_rows = two_tile ? fa_ws_kv_box_rows() : 128;
     CUtensorMap tq, tk, tv;
-    if (get_qkv_tmap(Q, p.S, p.H_local, p.d_h, &tq) || get_qkv_tmap(K, p.S, p.H_local, p.d_h, &tk) ||
-        get_qkv_tmap(V, p.S, p.H_local, p.d_h, &tv))
+    if (get_qkv_tmap(Q, p.S, p.H_local, p.d_h, 128, &tq) || get_qkv_tmap(K, p.S, p.H_local, p.d_h, kv_rows, &tk) ||
+        get_qkv_tmap(V, p.S, p.H_local, p.d_h, kv_rows, &tv))
         return 1;
 
     FaArgs a;
@@ -474,15 +504,12 @@ int fa_forward(const void* Q, const void* K, const void* V, void* O, int o_dtype
     a.status = kernel_status_word();
     a.band_blocks = (tile_counters == nullptr) ? (q_rows + 255) / 256 : band_rows / 256;
     // Nobody waits for particular rows of a launch without counters, so under a causal mask its longest work
-    // items (the last rows) go first and the launch ends on short ones; with counters rows complete in order.
-    a.heavy_first = (tile_counters == nullptr && p.causal && getenv("EFA_ATTN_ROW_ORDER") == nullptr) ? 1 : 0;
+    // items (the last rows) go first and the launch ends on short ones; with counters the caller says in which
+    // order it will wait for them (first rows first unless told otherwise).
+    a.heavy_first = heavy_first >= 0 ? (heavy_first ? 1 : 0) : ((tile_counters == nullptr && p.causal) ? 1 : 0);
 
     const bool f16 = (o_dtype == EFA_F16);
-    // d_h = 64 / 128 run on the warp-specialised two-tile kernel; EFA_ATTN_ONE_TILE=1 (a diagnostics
-    // switch, like the reference's --no_prio) keeps them on the one-tile kernel below for A/B timing.
-    static const bool one_tile_only = [] { const char* e = getenv("EFA_ATTN_ONE_TILE"); return e && e[0] == '1'; }();
-    if ((p.d_h == 64 || p.d_h == 128) && !one_tile_only)
-        return fa_forward_ws(tq, tk, tv, a, p.d_h, f16, reserve_sms, stream);
+    if (two_tile) return fa_forward_ws(tq, tk, tv, a, p.d_h, f16, reserve_sms, stream);
     dim3 grid(p.H_local * p.split, (q_rows + FA_BM - 1) / FA_BM);
     switch (p.d_h) {
         case 16:  return f16 ? launch_fa<16, true>(tq, tk, tv, a, grid, stream)  : launch_fa<16, false>(tq, tk, tv, a, grid, stream);
@@ -499,14 +526,15 @@ int fa_combine(const efa_flash_partials& part, void* O, int o_dtype, int row0, i
 {
     if (p.split <= 1) return 0;
     const int d_local = p.H_local * p.d_h;
-    const long total = (long)rows * (d_local / 2);
-    const int blocks = (int)((total + 255) / 256);
+    const int blocks = (rows + CB_ROWS - 1) / CB_ROWS;
+    const size_t smem = (size_t)CB_ROWS * p.H_local * p.split * sizeof(float);
+    if (smem > 48 * 1024) { set_error("flash_attn_tc_combine: H_local * split = %d is too large", p.H_local * p.split); return 2; }
     if (o_dtype == EFA_F16)
-        combine_splits_kernel<true><<<blocks, 256, 0, stream>>>(part.O_part, part.m_part, part.l_part, O,
-                                                                 row0, rows, part.rows, d_local, p.H_local, p.d_h, p.split);
+        combine_splits_kernel<true><<<blocks, 256, smem, stream>>>(part.O_part, part.m_part, part.l_part, O,
+                                                                   row0, rows, part.rows, d_local, p.H_local, p.d_h, p.split);
     else
-        combine_splits_kernel<false><<<blocks, 256, 0, stream>>>(part.O_part, part.m_part, part.l_part, O,
-                                                                  row0, rows, part.rows, d_local, p.H_local, p.d_h, p.split);
+        combine_splits_kernel<false><<<blocks, 256, smem, stream>>>(part.O_part, part.m_part, part.l_part, O,
+                                                                    row0, rows, part.rows, d_local, p.H_local, p.d_h, p.split);
     EFA_CUDA(cudaGetLastError());
     return 0;
 }

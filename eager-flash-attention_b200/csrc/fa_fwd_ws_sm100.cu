@@ -33,13 +33,6 @@
 
 #include <cmath>
 
-// Compile-time experiment switch: every n-th exponential on the FMA pipes (ex2_poly) instead of MUFU.
-// Measured on B200 with n = 4, 3, 2: 8 %, 5-10 % and 30 % slower than n = 0 at d_h = 64 and 128 alike, i.e. the
-// softmax warps are bound by instruction issue and latency, not by MUFU throughput. Off.
-#ifndef EFA_POLY_EVERY
-#define EFA_POLY_EVERY 0
-#endif
-
 // Compile-time experiment switch: scale-and-offset and the row sum on packed pairs (fma.rn.f32x2 / add.rn.f32x2,
 // two fp32 lanes per instruction, same rounding as the scalar forms), which takes a quarter of the instructions
 // out of the softmax loop. Not yet measured; off.
@@ -68,24 +61,6 @@ struct WsCfg {
     static constexpr int SMEM_BYTES = TILE_BYTES * (2 + 2 * NSTAGE) + 1024;
     static constexpr int TMEM_COLS  = 512;
 };
-
-// 2^x on the FMA and integer pipes instead of the special-function unit: round to the nearest integer
-// with the 1.5*2^23 trick, a degree-3 minimax polynomial for 2^f on [-0.5, 0.5] (relative error 7.5e-5,
-// an order of magnitude below the fp16 rounding P gets anyway), and the integer part added into the
-// exponent field. Only used when EFA_POLY_EVERY > 0.
-__device__ __forceinline__ __attribute__((unused)) float ex2_poly(float x)
-{
-    x = fmaxf(x, -126.f);
-    const float magic = 12582912.f;                 // 1.5 * 2^23: low mantissa bits of (x + magic) = round(x)
-    const float t = x + magic;
-    const float f = x - (t - magic);
-    float p = fmaf(0.05517166f, f, 0.24261113f);
-    p = fmaf(p, f, 0.69326097f);
-    p = fmaf(p, f, 0.99992806f);
-    return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
-}
-
-constexpr int kPolyEvery = EFA_POLY_EVERY;          // every n-th exponential uses ex2_poly (0 = none)
 
 __device__ __forceinline__ float max3(float a, float b, float c)
 {
@@ -449,9 +424,7 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ,
                         const float x0 = fmaf(__uint_as_float(su[c][2 * i]),     a.scale_log2e, -m_off);
                         const float x1 = fmaf(__uint_as_float(su[c][2 * i + 1]), a.scale_log2e, -m_off);
                         const float p0 = ex2(x0);
-                        float p1;
-                        if constexpr (kPolyEvery > 0) p1 = (((2 * i + 1) % (kPolyEvery > 0 ? kPolyEvery : 1)) == kPolyEvery - 1) ? ex2_poly(x1) : ex2(x1);
-                        else p1 = ex2(x1);
+                        const float p1 = ex2(x1);
                         ps0 += p0;
                         ps1 += p1;
                         pk[i] = pack_f16x2(p0, p1);
@@ -619,5 +592,7 @@ int fa_forward_ws(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMa
     set_error("fa_forward_ws: d_h=%d is not handled by the warp-specialised kernel", d_h);
     return 2;
 }
+
+int fa_ws_kv_box_rows() { return WS_BN; }
 
 }  // namespace efa

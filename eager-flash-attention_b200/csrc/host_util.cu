@@ -62,7 +62,24 @@ const DriverApi* driver_api()
         resolve("cuStreamWaitValue32", (void**)&api.cuStreamWaitValue32) ||
         resolve("cuStreamWriteValue32", (void**)&api.cuStreamWriteValue32) ||
         resolve("cuGetErrorString", (void**)&api.cuGetErrorString) ||
-        resolve("cuMemGetAddressRange", (void**)&api.cuMemGetAddressRange)) {
+        resolve("cuMemGetAddressRange", (void**)&api.cuMemGetAddressRange) ||
+        resolve("cuCtxGetDevice", (void**)&api.cuCtxGetDevice) ||
+        resolve("cuDeviceGetAttribute", (void**)&api.cuDeviceGetAttribute) ||
+        resolve("cuMemGetAllocationGranularity", (void**)&api.cuMemGetAllocationGranularity) ||
+        resolve("cuMemCreate", (void**)&api.cuMemCreate) ||
+        resolve("cuMemRelease", (void**)&api.cuMemRelease) ||
+        resolve("cuMemAddressReserve", (void**)&api.cuMemAddressReserve) ||
+        resolve("cuMemAddressFree", (void**)&api.cuMemAddressFree) ||
+        resolve("cuMemMap", (void**)&api.cuMemMap) ||
+        resolve("cuMemUnmap", (void**)&api.cuMemUnmap) ||
+        resolve("cuMemSetAccess", (void**)&api.cuMemSetAccess) ||
+        resolve("cuMemExportToShareableHandle", (void**)&api.cuMemExportToShareableHandle) ||
+        resolve("cuMemImportFromShareableHandle", (void**)&api.cuMemImportFromShareableHandle) ||
+        resolve("cuMulticastCreate", (void**)&api.cuMulticastCreate) ||
+        resolve("cuMulticastAddDevice", (void**)&api.cuMulticastAddDevice) ||
+        resolve("cuMulticastBindMem", (void**)&api.cuMulticastBindMem) ||
+        resolve("cuMulticastUnbind", (void**)&api.cuMulticastUnbind) ||
+        resolve("cuMulticastGetGranularity", (void**)&api.cuMulticastGetGranularity)) {
         state = -1;
         return nullptr;
     }

@@ -30,6 +30,24 @@ struct DriverApi {
     CUresult (*cuStreamWriteValue32)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
     CUresult (*cuGetErrorString)(CUresult, const char**);
     CUresult (*cuMemGetAddressRange)(CUdeviceptr*, size_t*, CUdeviceptr);
+    // virtual memory management and NVLink multicast objects (nvls_reduce.cu)
+    CUresult (*cuCtxGetDevice)(CUdevice*);
+    CUresult (*cuDeviceGetAttribute)(int*, CUdevice_attribute, CUdevice);
+    CUresult (*cuMemGetAllocationGranularity)(size_t*, const CUmemAllocationProp*, CUmemAllocationGranularity_flags);
+    CUresult (*cuMemCreate)(CUmemGenericAllocationHandle*, size_t, const CUmemAllocationProp*, unsigned long long);
+    CUresult (*cuMemRelease)(CUmemGenericAllocationHandle);
+    CUresult (*cuMemAddressReserve)(CUdeviceptr*, size_t, size_t, CUdeviceptr, unsigned long long);
+    CUresult (*cuMemAddressFree)(CUdeviceptr, size_t);
+    CUresult (*cuMemMap)(CUdeviceptr, size_t, size_t, CUmemGenericAllocationHandle, unsigned long long);
+    CUresult (*cuMemUnmap)(CUdeviceptr, size_t);
+    CUresult (*cuMemSetAccess)(CUdeviceptr, size_t, const CUmemAccessDesc*, size_t);
+    CUresult (*cuMemExportToShareableHandle)(void*, CUmemGenericAllocationHandle, CUmemAllocationHandleType, unsigned long long);
+    CUresult (*cuMemImportFromShareableHandle)(CUmemGenericAllocationHandle*, void*, CUmemAllocationHandleType);
+    CUresult (*cuMulticastCreate)(CUmemGenericAllocationHandle*, const CUmulticastObjectProp*);
+    CUresult (*cuMulticastAddDevice)(CUmemGenericAllocationHandle, CUdevice);
+    CUresult (*cuMulticastBindMem)(CUmemGenericAllocationHandle, size_t, CUmemGenericAllocationHandle, size_t, size_t, unsigned long long);
+    CUresult (*cuMulticastUnbind)(CUmemGenericAllocationHandle, CUdevice, size_t, size_t);
+    CUresult (*cuMulticastGetGranularity)(size_t*, const CUmulticastObjectProp*, CUmulticastGranularity_flags);
 };
 // nullptr (with the error recorded) when the driver is not available.
 const DriverApi* driver_api();

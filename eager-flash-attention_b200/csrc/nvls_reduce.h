@@ -1,0 +1,32 @@
+// Sum AllReduce of fp16 partial sums through an NVLink multicast object (NVSwitch reduces in the
+// switch, fp32 accumulation, one rounding): the third way to do allreduce() of eager-flash-attention
+// (run_drivers.cu:26-30) beside NCCL and the fused peer-memory kernel.
+#pragma once
+
+#include "runtime.h"
+
+namespace efa {
+
+// 1 when this path can run the problem on this machine; otherwise 0 and *why says what is in the way.
+// Collective when it has to ask the devices (every rank gets the same answer).
+int nvls_supported(efa_ctx* c, const efa_params& p, const char** why);
+
+// Symmetric memory for S*d fp16 partial sums and S*d fp16 results, bound to a multicast object over all
+// ranks of the context. Collective; a no-op when the region in place is large enough.
+int nvls_prepare(efa_ctx* c, const efa_params& p);
+
+// Where the projection writes this rank's partial sums ([S][d] fp16, local memory), and where the reduced
+// rows appear on every rank.
+void* nvls_send_buf(efa_ctx* c);
+void* nvls_result_buf(efa_ctx* c);
+
+// Reduce elements [first, first + n) of the partial sums over all ranks into the same elements of the result
+// buffer of EVERY rank. One kernel on `stream`; `slot` (< EFA_MAX_COMM) names the stream's barrier flags, so
+// calls on different streams may overlap as long as they use different slots. Collective: every rank makes
+// the same sequence of calls per slot.
+int nvls_allreduce(efa_ctx* c, int slot, size_t first, size_t n, cudaStream_t stream);
+
+// Unmaps and unbinds (collective when the region exists). Called by efa_destroy_ctx.
+void nvls_destroy(efa_ctx* c);
+
+}  // namespace efa

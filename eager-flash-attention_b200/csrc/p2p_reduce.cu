@@ -68,8 +68,7 @@ constexpr int PR_A_BYTES = PR_BM * PR_BK * 2;            // 16 KB
 constexpr int PR_B_BOX = PR_BK * 64 * 2;                 // one [64 k][64 n] box of W_O, 8 KB
 constexpr int PR_OUT_BYTES = PR_BM * 128 * 2;            // 32 KB staging of one 128x128 fp16 output tile
 constexpr int PR_THREADS = 320;   // producer warp, MMA warp, 4 epilogue warps, 4 reduction warps
-constexpr unsigned long long kFlagWaitNs = 10000000000ull;   // 10 s: waits on the attention kernel or on a peer
-constexpr unsigned long long kChainWaitNs = 12000000000ull;  // waits inside the CTA that depend on such a wait
+constexpr unsigned long long kChainSlackNs = 2000000000ull;  // waits inside the CTA that depend on a flag wait get this much longer
 
 // BN = accumulator width. 256 keeps the tensor pipe fed: with 128 the two shared-memory operand reads
 // of every MMA plus the TMA writes of the next stage exceed the shared-memory bandwidth and the MMAs run
@@ -96,6 +95,8 @@ struct PrArgs {
     int* done_peer[8];
     __half* out_peer[8];
     int* status;
+    unsigned long long flag_wait_ns;   // limit of a wait on the attention kernel or on a peer
+    unsigned long long chain_wait_ns;  // limit of the waits inside the CTA that depend on such a wait
 };
 
 __device__ __forceinline__ int ld_acquire_gpu(const int* p)
@@ -115,16 +116,18 @@ __device__ __forceinline__ void red_add_sys(int* p, int v)
     asm volatile("red.release.sys.global.add.s32 [%0], %1;" :: "l"(p), "r"(v) : "memory");
 }
 
-// Poll `*p >= target` with a deadline. scope_sys: the writer is another GPU.
-__device__ __forceinline__ bool wait_flag(const int* p, int target, bool scope_sys, volatile int* abort_word, int site)
+// Poll until `*p` has reached `target` (counters only grow; the comparison survives their wrap-around), with a
+// deadline. scope_sys: the writer is another GPU.
+__device__ __forceinline__ bool wait_flag(const int* p, int target, bool scope_sys, volatile int* abort_word, int site,
+                                          unsigned long long limit_ns)
 {
     const unsigned long long t0 = globaltimer_ns();
     int spins = 0;
     while (true) {
         const int v = scope_sys ? ld_acquire_sys(p) : ld_acquire_gpu(p);
-        if (v >= target) return true;
+        if ((int)((unsigned)v - (unsigned)target) >= 0) return true;
         if (*abort_word != 0) return false;
-        if ((++spins & 15) == 0 && globaltimer_ns() - t0 > kFlagWaitNs) { *abort_word = site; return false; }
+        if ((++spins & 15) == 0 && globaltimer_ns() - t0 > limit_ns) { *abort_word = site; return false; }
         __nanosleep(spins < 64 ? 100 : 500);
     }
 }
@@ -213,7 +216,7 @@ tile_proj_reduce_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                 if (rb > ready_rb) {
                     const int t0 = (rb * PR_BM) / a.tile;
                     const int t1 = min(rb * PR_BM + PR_BM - 1, a.S - 1) / a.tile;
-                    for (int t = t0; t <= t1 && ok; t++) ok = wait_flag(a.counters + t, a.tile_target, false, &abort_word, 41);
+                    for (int t = t0; t <= t1 && ok; t++) ok = wait_flag(a.counters + t, a.tile_target, false, &abort_word, 41, a.flag_wait_ns);
                     if (!ok) break;
                     asm volatile("fence.proxy.async.global;" ::: "memory");   // O rows were written by generic-proxy stores
                     ready_rb = rb;
@@ -223,7 +226,7 @@ tile_proj_reduce_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                     for (int kb = 0; kb < num_k; kb++, kcount++) {
                         const int s = (int)(kcount % NST);
                         const long use = kcount / NST;
-                        if (use > 0 && !mbar_wait(&bar_empty[s], (uint32_t)((use - 1) & 1), &abort_word, 42, kChainWaitNs)) { ok = false; break; }
+                        if (use > 0 && !mbar_wait(&bar_empty[s], (uint32_t)((use - 1) & 1), &abort_word, 42, a.chain_wait_ns)) { ok = false; break; }
                         uint8_t* sa = smem + s * C::STAGE;
                         uint8_t* sb = sa + PR_A_BYTES;
                         mbar_expect_tx(&bar_full[s], C::STAGE);
@@ -245,12 +248,12 @@ tile_proj_reduce_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             for (; item < my_items && ok; item++) {
                 const int b = (int)(item & 1);
                 const long use = item >> 1;
-                if (use > 0) ok = mbar_wait(&acc_empty[b], (uint32_t)((use - 1) & 1), &abort_word, 43, kChainWaitNs);
+                if (use > 0) ok = mbar_wait(&acc_empty[b], (uint32_t)((use - 1) & 1), &abort_word, 43, a.chain_wait_ns);
                 if (!ok) break;
                 tc_fence_after_sync();
                 for (int kb = 0; kb < num_k; kb++, kcount++) {
                     const int s = (int)(kcount % NST);
-                    ok = mbar_wait(&bar_full[s], (uint32_t)((kcount / NST) & 1), &abort_word, 44, kChainWaitNs);
+                    ok = mbar_wait(&bar_full[s], (uint32_t)((kcount / NST) & 1), &abort_word, 44, a.chain_wait_ns);
                     if (!ok) break;
                     tc_fence_after_sync();
                     const uint32_t sa = smem_u32(smem + s * C::STAGE);
@@ -270,7 +273,7 @@ tile_proj_reduce_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         bool alive = true;
         for (long ri = g; ri < n_red && alive; ri += G) {
             const int rb = (int)(ri / nrg), cg = (int)(ri % nrg);
-            if (et == 0) wait_flag(a.arrive_peer[a.rank] + rb, a.arrive_target, true, &abort_word, 45);
+            if (et == 0) wait_flag(a.arrive_peer[a.rank] + rb, a.arrive_target, true, &abort_word, 45, a.flag_wait_ns);
             if (bar_or_reduce(abort_word != 0)) { alive = false; break; }
             for (int m = cg * a.GS; m < (cg + 1) * a.GS; m++) {
                 const __half* src = a.stage_peer[a.rank] + ((size_t)rb * a.NBR + m) * a.R * (PR_BM * 128);
@@ -324,7 +327,7 @@ tile_proj_reduce_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         // the output of this rank is complete when every owner has delivered every row block
         if (alive && a.R > 1 && et == 0)
             for (int rb = g; rb < a.nrb; rb += G)
-                if (!wait_flag(a.done_peer[a.rank] + rb, a.done_target, true, &abort_word, 47)) break;
+                if (!wait_flag(a.done_peer[a.rank] + rb, a.done_target, true, &abort_word, 47, a.flag_wait_ns)) break;
     } else {
         // ---- epilogue warps (128 threads); TMEM lane quarter = warp % 4
         const int et = tid - 64;                       // 0..127
@@ -341,7 +344,7 @@ tile_proj_reduce_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                 const int n0 = gi * a.GS + j * C::CB;
                 const int b = (int)(item & 1);
                 // warp-uniform decision: the tensor-memory loads below need whole warps
-                const bool got = __all_sync(0xffffffffu, mbar_wait(&acc_full[b], (uint32_t)((item >> 1) & 1), &abort_word, 46, kChainWaitNs));
+                const bool got = __all_sync(0xffffffffu, mbar_wait(&acc_full[b], (uint32_t)((item >> 1) & 1), &abort_word, 46, a.chain_wait_ns));
                 if (got) tc_fence_after_sync();
                 #pragma unroll 1
                 for (int h = 0; h < C::CB && alive; h++) {
@@ -538,13 +541,12 @@ int p2p_prepare(efa_ctx* c, const efa_params& p, void* output)
 
 int* p2p_counters(efa_ctx* c) { return c->p2p ? c->p2p->counters : nullptr; }
 
-// Launch the persistent kernel for this run (once; `t` is ignored beyond the first call).
-int p2p_tile(efa_ctx* c, const efa_params& p, const efa_weights& w, const void* O_all, int t, int* launches)
+// Launch the persistent kernel for this run.
+int p2p_launch(efa_ctx* c, const efa_params& p, const efa_weights& w, const void* O_all, int* launches)
 {
     P2PState* st = c->p2p;
-    if (!st || st->S != p.S) { set_error("p2p_tile without p2p_prepare"); return 2; }
+    if (!st || st->S != p.S) { set_error("p2p_launch without p2p_prepare"); return 2; }
     if (st->launched_this_run) return 0;
-    (void)t;
     if (st->tm_O != O_all || st->tm_W != w.W_O) {
         unsigned long long dimsA[2] = {(unsigned long long)p.d_local, (unsigned long long)p.S};
         unsigned long long strA[1] = {(unsigned long long)p.d_local * 2ull};
@@ -562,10 +564,12 @@ int p2p_tile(efa_ctx* c, const efa_params& p, const efa_weights& w, const void* 
     a.nrb = (p.S + 127) / 128; a.NB = p.d / 128; a.NBR = a.NB / p.R;
     a.tile = p.tile;
     a.GS = (p.R > 1) ? a.NBR : 1;
-    if (const char* e = getenv("EFA_P2P_GROUP")) { const int v = atoi(e); if (v >= 1 && a.NBR % v == 0) a.GS = v; }
-    a.tile_target = (int)(st->epoch * st->target);
-    a.arrive_target = (int)(st->epoch * p.R * (a.NBR / a.GS));
-    a.done_target = (int)(st->epoch * p.R * (a.NBR / a.GS));
+    // Counters and flags only grow; the targets wrap with them (see wait_flag).
+    a.tile_target = (int)(unsigned)((unsigned long long)st->epoch * (unsigned long long)st->target);
+    a.arrive_target = (int)(unsigned)((unsigned long long)st->epoch * (unsigned long long)(p.R * (a.NBR / a.GS)));
+    a.done_target = a.arrive_target;
+    a.flag_wait_ns = c->wait_limit_ns;
+    a.chain_wait_ns = c->wait_limit_ns + kChainSlackNs;
     a.counters = st->counters;
     for (int r = 0; r < p.R; r++) {
         a.stage_peer[r] = st->stage_peer[r];
@@ -586,7 +590,7 @@ int p2p_tile(efa_ctx* c, const efa_params& p, const efa_weights& w, const void* 
         G = (int)(148.0 * proj / (attn + proj) * 0.9 + 0.5);   // measured: the projection runs at a higher fraction of peak than attention
         if (G < 6) G = 6;
         if (G > 48) G = 48;
-        if (const char* e = getenv("EFA_P2P_CTAS")) { const int v = atoi(e); if (v >= 1 && v <= 148) G = v; }
+        if (p.reduce_ctas >= 1 && p.reduce_ctas <= 148) G = p.reduce_ctas;
         const long groups = (long)a.nrb * (a.NB / a.GS);
         if (G > groups) G = (int)groups;
     }
@@ -596,8 +600,6 @@ int p2p_tile(efa_ctx* c, const efa_params& p, const efa_weights& w, const void* 
     st->launched_this_run = true;
     return 0;
 }
-
-int p2p_finish(efa_ctx*, const efa_params&) { return 0; }
 
 void p2p_destroy(efa_ctx* c)
 {

@@ -13,11 +13,9 @@ int* p2p_counters(efa_ctx* c);
 
 // Exchange IPC handles of the staging buffers for this shape (collective; cached in the context).
 int p2p_prepare(efa_ctx* c, const efa_params& p, void* output);
-// Launch the persistent projection + reduction kernel of this run on the projection stream
-// (first call of a run launches; later calls in the same run do nothing). O_all: fp16 [S][d_local].
-int p2p_tile(efa_ctx* c, const efa_params& p, const efa_weights& w, const void* O_all, int t, int* launches);
-// Enqueue the final hand-shake that makes every rank's output complete.
-int p2p_finish(efa_ctx* c, const efa_params& p);
+// Launch the persistent projection + reduction kernel of this run on the projection stream.
+// O_all: fp16 [S][d_local].
+int p2p_launch(efa_ctx* c, const efa_params& p, const efa_weights& w, const void* O_all, int* launches);
 void p2p_destroy(efa_ctx* c);
 
 }  // namespace efa

@@ -219,6 +219,8 @@ extern "C" int efa_make_params(efa_params* out, int S, int d, int H, int tile, i
     p.reduce = EFA_REDUCE_NCCL;
     p.group_tiles = 0;
     p.proj_f32 = 0;
+    p.row_order = EFA_ROWS_AUTO;
+    p.reduce_ctas = 0; p.band_rows = 0; p.reserve_sms = 0; p.trace = 0;
     const float scale = p.d_h > 0 ? 1.0f / sqrtf((float)p.d_h) : 0.f;
     p.flash_tc = efa_flash_params{S, p.d_h, p.H_local, split, causal, scale};
     *out = p;
@@ -242,37 +244,48 @@ extern "C" int efa_blocks_per_tile(const efa_params* p)
     return (p->tile / 64) * p->H_local * p->split;
 }
 
-extern "C" int efa_stream_plan(const efa_params* p, efa_stream_group* groups, int capacity, int* band_rows)
+extern "C" int efa_stream_plan(const efa_params* p, efa_stream_group* groups, int capacity, int* band_rows, int* descending)
 {
     if (!p || p->tile <= 0 || p->num_tiles <= 0) { set_error("efa_stream_plan: invalid params"); return -1; }
+    const bool desc = p->row_order == EFA_ROWS_DESCENDING || (p->row_order == EFA_ROWS_AUTO && p->causal);
+    if (descending) *descending = desc ? 1 : 0;
     const bool auto_groups = p->group_tiles <= 0;
     int gt = p->group_tiles;
     if (auto_groups) { gt = (p->S / 8) / p->tile; if (gt < 1) gt = 1; }
     if (gt > p->num_tiles) gt = p->num_tiles;
-    int n = 0;
+    int n = 0, smallest = p->num_tiles;
+    // Laid out in time order over positions 0 .. num_tiles: position x is tile x (ascending) or tile
+    // num_tiles - 1 - x (descending).
     for (int t0 = 0; t0 < p->num_tiles; n++) {
         int nt = (t0 + gt <= p->num_tiles) ? gt : p->num_tiles - t0;
         if (auto_groups && gt >= 4 && t0 + gt >= p->num_tiles) {
-            // the last eighth: S/16, S/32, S/32 rows
+            // the eighth that completes last: S/16, S/32, S/32 rows
             const int left = p->num_tiles - t0;
             nt = (left > gt / 2) ? gt / 2 : (left > gt / 4 ? left - gt / 4 : left);
             if (nt < 1) nt = left;
         }
         if (groups) {
             if (n >= capacity) { set_error("efa_stream_plan: more than %d groups", capacity); return -1; }
-            groups[n].first_tile = t0;
+            groups[n].first_tile = desc ? p->num_tiles - t0 - nt : t0;
             groups[n].ntiles = nt;
         }
+        if (nt < smallest) smallest = nt;
         t0 += nt;
     }
     if (band_rows) {
-        // Rows only have to complete group by group, so the attention kernel may order its work in bands no
-        // longer than the smallest group: S/16 rows with automatic grouping (the two smallest groups then
-        // complete together), at most 2048, whole 256-row blocks, and no bands below 512 rows.
-        int b = auto_groups ? p->S / 16 : p->group_tiles * p->tile;
+        // Rows only have to complete group by group, so the attention kernel may order its work in bands no longer
+        // than the smallest group (whole 256-row blocks, at most 2048 rows, none below 512). Bands exist for the L2:
+        // in strict row order every local head's K and V are live at once; when they fit in the L2 anyway (half of
+        // it is assumed to be available to them) there is nothing to gain and strict order is kept.
+        int b = smallest * p->tile;
+        if (auto_groups && b < p->S / 16) b = p->S / 16;      // the two smallest groups may complete together
         b = (b / 256) * 256;
         if (b > 2048) b = 2048;
         if (b < 512) b = 0;
+        const double kv_bytes = 2.0 * (double)p->H_local * p->S * p->d_h * 2.0;
+        if (kv_bytes <= 80e6) b = 0;
+        if (p->band_rows > 0) b = (p->band_rows / 256) * 256;
+        if (p->band_rows < 0) b = 0;
         *band_rows = b;
     }
     return n;
@@ -326,13 +339,22 @@ extern "C" int efa_make_ctx(efa_ctx** out, const efa_world* world, int ncomm, in
     return 0;
 }
 
-namespace efa { void p2p_destroy(efa_ctx* c); }
+namespace efa { void p2p_destroy(efa_ctx* c); void nvls_destroy(efa_ctx* c); }
+
+extern "C" int efa_ctx_set_wait_limit_ms(efa_ctx* c, double device_ms, double host_ms)
+{
+    if (!c) { set_error("efa_ctx_set_wait_limit_ms: null context"); return 2; }
+    if (device_ms > 0.0) c->wait_limit_ns = (unsigned long long)(device_ms * 1e6);
+    if (host_ms > 0.0) c->host_wait_limit_ms = host_ms;
+    return 0;
+}
 
 extern "C" int efa_destroy_ctx(efa_ctx* c)
 {
     if (!c) return 0;
     cudaDeviceSynchronize();
     p2p_destroy(c);
+    nvls_destroy(c);
     for (int i = 0; i < c->ncomm; i++) {
         if (c->nccls[i] && nccl_api()) nccl_api()->CommDestroy(c->nccls[i]);
         if (c->comm_streams[i]) cudaStreamDestroy(c->comm_streams[i]);

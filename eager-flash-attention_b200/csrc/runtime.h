@@ -11,6 +11,7 @@
 #define EFA_MAX_COMM 8   /* MAX_COMM, attn_defs.cuh:90 */
 
 struct P2PState;   // peer-mapped staging of the fused reduction (p2p_reduce.cu)
+struct NvlsState;  // symmetric memory bound to an NVLink multicast object (nvls_reduce.cu)
 
 struct efa_ctx {
     efa_world    world;
@@ -37,6 +38,13 @@ struct efa_ctx {
     cudaStream_t h2d_stream = nullptr, d2h_stream = nullptr;   // copies of the pipelined host-buffer path
 
     P2PState* p2p = nullptr;
+    NvlsState* nvls = nullptr;
+    int nvls_ctas = 16;                                        // thread blocks of one multicast reduction (fixed per context)
+
+    // Limit of every device-side wait on another kernel or another rank (tile counters, arrival flags, barrier
+    // flags), and of the host's wait for a stream; efa_ctx_set_wait_limit_ms changes both.
+    unsigned long long wait_limit_ns = 10000000000ull;         // 10 s
+    double             host_wait_limit_ms = 120000.0;          // 120 s
 };
 
 namespace efa {

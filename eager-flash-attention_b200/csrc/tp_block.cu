@@ -8,6 +8,7 @@
 #include "fa_fwd_sm100.cuh"
 #include "host_util.h"
 #include "nccl_dyn.h"
+#include "nvls_reduce.h"
 #include "p2p_reduce.h"
 
 #include <chrono>
@@ -67,9 +68,18 @@ struct Run {
     const char*   out_base = nullptr;   // the output buffer `residual` runs parallel to
     int launches = 0;
 
-    // Partial sums and output are fp16, or fp32 with proj_f32 (the reference's types).
+    // `output` is fp16, or fp32 with proj_f32 (the reference's types).
     size_t esz() const { return p.proj_f32 ? sizeof(float) : sizeof(__half); }
     size_t row_bytes() const { return (size_t)p.d * esz(); }
+    // The partial sums that are reduced. NCCL adds fp16 values in fp16, one rounding per hop, which with more
+    // than two ranks exceeds what one final rounding costs (3.5e-3 against 1.7e-3 at outputs of magnitude 3.4
+    // with eight ranks). So with more than two ranks the NCCL path reduces the fp32 accumulators and rounds the
+    // sum once (the reference reduces fp32 too, run_drivers.cu:26-30); with two ranks one fp16 addition is one rounding
+    // either way. The multicast path accumulates in fp32 inside the switch and keeps fp16 on the wire.
+    bool wire_f32() const { return p.proj_f32 || (p.reduce == EFA_REDUCE_NCCL && p.R > 2 && !p.skip_comm); }
+    bool nvls() const { return p.reduce == EFA_REDUCE_NVLS && !p.skip_comm && p.R > 1; }
+    size_t send_row_bytes() const { return (size_t)p.d * (wire_f32() ? sizeof(float) : sizeof(__half)); }
+    char* send_base() const { return static_cast<char*>(nvls() ? nvls_send_buf(c) : c->send_buf); }
 
     efa_flash_partials ws(int rows) const
     {
@@ -80,8 +90,9 @@ struct Run {
 
     // Attention kernel only (launch_attention_raw, attn_main.cu:234-245).
     // ws_row0: workspace row that the launch's first row maps to (split partials of several launches side by side).
+    // heavy_first: -1 = the kernel's default (last rows first when nobody waits for counters), 0 / 1 = first / last rows first.
     int attention_raw(__half* O, int ws_rows, int q_start, int q_rows, cudaStream_t s, int* counters, int tile_rows,
-                      int reserve_sms = 0, int band_rows = 0, int ws_row0 = 0)
+                      int reserve_sms = 0, int band_rows = 0, int ws_row0 = 0, int heavy_first = -1)
     {
         efa_flash_partials q = ws(ws_rows);
         if (q.O_part && ws_row0 > 0) {
@@ -91,7 +102,7 @@ struct Run {
         }
         launches++;
         return fa_forward(w.Qh, w.Kh, w.Vh, O, EFA_F16, &q, q_start, q_rows, p.flash_tc, s, counters, tile_rows, reserve_sms,
-                          band_rows);
+                          band_rows, heavy_first);
     }
     // launch_combine (attn_main.cu:247-252): no-op when split == 1.
     int combine(__half* O, int ws_rows, int row0, int rows, cudaStream_t s)
@@ -105,27 +116,43 @@ struct Run {
         if (attention_raw(O, ws_rows, q_start, q_rows, s, nullptr, 0)) return 1;
         return combine(O, ws_rows, 0, q_rows, s);
     }
-    // project (attn_main.cu:262-273) on the projection stream.
+    // project (attn_main.cu:262-273) on the projection stream; `out` is a place in the send buffer.
     int project(const __half* O_tile, void* out, int rows)
     {
         if (p.skip_proj) return 0;
         launches++;
-        return project_f16(O_tile, w.W_O, out, rows, p.d_local, p.d, c->proj_stream, p.proj_f32 ? EFA_F32 : EFA_F16);
+        return project_f16(O_tile, w.W_O, out, rows, p.d_local, p.d, c->proj_stream, wire_f32() ? EFA_F32 : EFA_F16);
     }
-    // allreduce (run_drivers.cu:26-30): communicator slot `slot`, sum of n elements (fp16, or fp32 with proj_f32).
-    int allreduce(int slot, const void* send, void* recv, size_t n)
+    // allreduce (run_drivers.cu:26-30): sum of n partial sums at `send` (a place in the send buffer) over the ranks
+    // into `recv` (a place in `output`), on communicator / stream `slot`.
+    int allreduce(int slot, void* send, void* recv, size_t n)
     {
         if (p.skip_comm) return 0;
-        const NcclApi* nccl = nccl_api();
-        if (!nccl) return 1;
-        ncclResult_t r = nccl->AllReduce(send, recv, n, p.proj_f32 ? ncclFloat : ncclHalf, ncclSum, c->nccls[slot],
-                                         c->comm_streams[slot]);
-        if (r != ncclSuccess) { set_error("ncclAllReduce: %s", nccl->GetErrorString(r)); return 1; }
+        cudaStream_t cs = c->comm_streams[slot];
+        if (nvls()) {
+            // the switch sums the ranks' send buffers into every rank's result buffer; one local copy to `output`
+            const size_t first = (size_t)(static_cast<char*>(send) - send_base()) / sizeof(__half);
+            launches++;
+            if (nvls_allreduce(c, slot, first, n, cs)) return 1;
+            EFA_CUDA(cudaMemcpyAsync(recv, static_cast<char*>(nvls_result_buf(c)) + first * sizeof(__half), n * sizeof(__half),
+                                     cudaMemcpyDeviceToDevice, cs));
+        } else {
+            const NcclApi* nccl = nccl_api();
+            if (!nccl) return 1;
+            const bool f32 = wire_f32();
+            void* dst = (f32 && !p.proj_f32) ? send : recv;          // fp32 sum in place, rounded into `output` below
+            ncclResult_t r = nccl->AllReduce(send, dst, n, f32 ? ncclFloat : ncclHalf, ncclSum, c->nccls[slot], cs);
+            if (r != ncclSuccess) { set_error("ncclAllReduce: %s", nccl->GetErrorString(r)); return 1; }
+            if (f32 && !p.proj_f32) {
+                launches++;
+                if (convert_f32_to_f16_dev(static_cast<const float*>(send), recv, n, cs)) return 1;
+            }
+        }
         if (residual) {
             // consume the rows where they landed, on the stream that reduced them
             launches++;
             const size_t first = (size_t)(static_cast<const char*>(recv) - out_base) / sizeof(__half);   // fp16 output only
-            return add_residual(static_cast<__half*>(recv), residual + first, n, c->comm_streams[slot]);
+            return add_residual(static_cast<__half*>(recv), residual + first, n, cs);
         }
         return 0;
     }
@@ -136,7 +163,7 @@ struct Run {
 // value from another stream so that every pending wait is released, and an error is returned.
 int sync_stream(efa_ctx* c, cudaStream_t s, int* counters, size_t ncounters)
 {
-    const double deadline_ms = 120000.0;
+    const double deadline_ms = c->host_wait_limit_ms;
     const double t0 = now_ms();
     long spins = 0;
     while (true) {
@@ -157,7 +184,7 @@ int sync_stream(efa_ctx* c, cudaStream_t s, int* counters, size_t ncounters)
             cudaStreamDestroy(rescue);
         }
     }
-    set_error("stream did not finish within %.0f s; pending tile waits were released", deadline_ms / 1e3);
+    set_error("stream did not finish within %.1f s; pending tile waits were released", deadline_ms / 1e3);
     return 4;
 }
 
@@ -183,10 +210,12 @@ int finish_timing(efa_ctx* c, double t0, efa_run_stats* st, bool attn_events, bo
     return 0;
 }
 
-int scratch(efa_ctx* c, const efa_params& p, size_t o_rows, size_t send_rows, size_t ncounters, size_t ws_rows, size_t nevents)
+int scratch(efa_ctx* c, const Run& r, size_t o_rows, size_t send_rows, size_t ncounters, size_t ws_rows, size_t nevents)
 {
+    const efa_params& p = r.p;
     if (o_rows && ensure_bytes(&c->O_all, &c->O_all_bytes, o_rows * p.d_local * sizeof(__half))) return 1;
-    if (send_rows && ensure_bytes(&c->send_buf, &c->send_bytes, send_rows * p.d * (p.proj_f32 ? sizeof(float) : sizeof(__half)))) return 1;
+    if (r.nvls()) { if (nvls_prepare(c, p)) return 1; }
+    else if (send_rows && ensure_bytes(&c->send_buf, &c->send_bytes, send_rows * r.send_row_bytes())) return 1;
     if (ncounters) {
         size_t have = c->counters_n * sizeof(int);
         if (ensure_bytes((void**)&c->counters, &have, ncounters * sizeof(int))) return 1;
@@ -212,7 +241,7 @@ int scratch(efa_ctx* c, const efa_params& p, size_t o_rows, size_t send_rows, si
 int run_attn_only(Run& r, efa_run_stats* st, bool tiled)
 {
     efa_ctx* c = r.c; const efa_params& p = r.p;
-    if (scratch(c, p, p.S, 0, 0, tiled ? p.tile : p.S, 0)) return 1;
+    if (scratch(c, r, p.S, 0, 0, tiled ? p.tile : p.S, 0)) return 1;
     __half* O_all = static_cast<__half*>(c->O_all);
     if (world_barrier(c->world)) return 1;
     const double t0 = now_ms();
@@ -232,9 +261,9 @@ int run_attn_only(Run& r, efa_run_stats* st, bool tiled)
 int run_megatron(Run& r, char* output, efa_run_stats* st)
 {
     efa_ctx* c = r.c; const efa_params& p = r.p;
-    if (scratch(c, p, p.S, p.S, 0, p.S, 2)) return 1;
+    if (scratch(c, r, p.S, p.S, 0, p.S, 2)) return 1;
     __half* O_all = static_cast<__half*>(c->O_all);
-    char* send_buf = static_cast<char*>(c->send_buf);
+    char* send_buf = r.send_base();
     cudaEvent_t attn_done = c->events[0], proj_done = c->events[1];
 
     if (world_barrier(c->world)) return 1;
@@ -260,9 +289,9 @@ int run_megatron(Run& r, char* output, efa_run_stats* st)
 int run_sync(Run& r, char* output, efa_run_stats* st)
 {
     efa_ctx* c = r.c; const efa_params& p = r.p;
-    if (scratch(c, p, p.tile, p.tile, 0, p.tile, 0)) return 1;
+    if (scratch(c, r, p.tile, p.tile, 0, p.tile, 0)) return 1;
     __half* O_tile = static_cast<__half*>(c->O_all);
-    char* send_buf = static_cast<char*>(c->send_buf);
+    char* send_buf = r.send_base();
     if (world_barrier(c->world)) return 1;
     const double t0 = now_ms();
     for (int t = 0; t < p.num_tiles; t++) {
@@ -284,9 +313,9 @@ int run_overlap(Run& r, char* output, efa_run_stats* st)
 {
     efa_ctx* c = r.c; const efa_params& p = r.p;
     const int nbuf = p.nbuf;
-    if (scratch(c, p, (size_t)nbuf * p.tile, (size_t)nbuf * p.tile, 0, p.tile, (size_t)3 * nbuf)) return 1;
+    if (scratch(c, r, (size_t)nbuf * p.tile, (size_t)nbuf * p.tile, 0, p.tile, (size_t)3 * nbuf)) return 1;
     __half* O_buf = static_cast<__half*>(c->O_all);
-    char* S_buf = static_cast<char*>(c->send_buf);
+    char* S_buf = r.send_base();
     auto attn_done = [&](int b) { return c->events[3 * b]; };
     auto proj_done = [&](int b) { return c->events[3 * b + 1]; };
     auto comm_done = [&](int b) { return c->events[3 * b + 2]; };
@@ -296,7 +325,7 @@ int run_overlap(Run& r, char* output, efa_run_stats* st)
     for (int t = 0; t < p.num_tiles; t++) {
         const int b = t % nbuf;
         __half* O_t = O_buf + (size_t)b * p.tile * p.d_local;
-        char* S_t = S_buf + (size_t)b * p.tile * r.row_bytes();
+        char* S_t = S_buf + (size_t)b * p.tile * r.send_row_bytes();
         if (t >= nbuf) EFA_CUDA(cudaStreamWaitEvent(c->compute_stream, proj_done(b), 0));
         if (r.attention(O_t, p.tile, t * p.tile, p.tile, c->compute_stream)) return 1;
         EFA_CUDA(cudaEventRecord(attn_done(b), c->compute_stream));
@@ -326,26 +355,24 @@ int run_stream(Run& r, char* output, efa_run_stats* st)
     efa_ctx* c = r.c; const efa_params& p = r.p;
     const DriverApi* api = driver_api();
     if (!api) return 1;
-    if (scratch(c, p, p.S, p.S, p.num_tiles, p.S, (size_t)p.num_tiles + 1)) return 1;
+    if (scratch(c, r, p.S, p.S, p.num_tiles, p.S, (size_t)p.num_tiles + 1)) return 1;
     __half* O_all = static_cast<__half*>(c->O_all);
-    char* send_buf = static_cast<char*>(c->send_buf);
+    char* send_buf = r.send_base();
     int* counters = c->counters;
     const int target = efa_blocks_per_tile(&p);
     cudaEvent_t reset_done = c->events[p.num_tiles];
     const bool fused = (p.reduce == EFA_REDUCE_P2P) && !p.skip_comm && !p.skip_proj;
-    // Launch plan (efa_stream_plan): groups of consecutive tiles per projection + AllReduce launch, and the band
-    // of rows within which the attention kernel may reorder its work (better K/V reuse in L2 than strict row
-    // order). Measured (benchmark shape, one rank, ms per block): strict order 10.4, bands of 1024 / 2048 /
-    // 4096 / 8192 rows 10.0 / 9.6 / 9.8 / 9.7.
+    // Launch plan (efa_stream_plan): groups of consecutive tiles per projection + reduction launch in the order in
+    // which they complete, and the band of rows within which the attention kernel may reorder its work (better
+    // K/V reuse in L2 than strict row order when the local heads' K and V exceed the L2).
     std::vector<efa_stream_group> groups(p.num_tiles);
-    int band_rows = 0;
-    const int ngroups = efa_stream_plan(&p, groups.data(), p.num_tiles, &band_rows);
+    int band_rows = 0, descending = 0;
+    const int ngroups = efa_stream_plan(&p, groups.data(), p.num_tiles, &band_rows, &descending);
     if (ngroups < 0) return 1;
-    if (const char* e = getenv("EFA_BAND_ROWS")) band_rows = atoi(e);
-    // EFA_TRACE=1: timing events around every group (counters reached, projection done, reduction done) and a
+    // p.trace: timing events around every group (counters reached, projection done, reduction done) and a
     // timeline on stderr after the run, relative to the start of the attention kernel. Diagnostic; the events
     // cost a few microseconds each, so traced runs are not benchmark numbers.
-    const bool trace = getenv("EFA_TRACE") != nullptr && !fused;
+    const bool trace = p.trace != 0 && !fused;
     if (trace && ensure_trace_events(c, (size_t)3 * ngroups)) return 1;
     if (fused) {
         // One persistent kernel does projection and reduction of every tile beside the attention kernel:
@@ -353,14 +380,14 @@ int run_stream(Run& r, char* output, efa_run_stats* st)
         // launched first: the first launch of a kernel may have to load its code, which can wait for
         // running kernels to drain, and a kernel that spins on the attention kernel's counters must
         // never be what that load waits for. The persistent CTAs (high-priority stream) take SMs as
-        // the first attention CTAs retire.
+        // the first attention CTAs retire. It takes the row blocks first to last, so the attention kernel does too.
         if (p2p_prepare(c, p, output)) return 1;
         if (world_barrier(c->world)) return 1;
         const double t0f = now_ms();
         EFA_CUDA(cudaEventRecord(c->ev_t0, c->compute_stream));
-        if (r.attention_raw(O_all, p.S, 0, p.S, c->compute_stream, p2p_counters(c), p.tile)) return 1;
+        if (r.attention_raw(O_all, p.S, 0, p.S, c->compute_stream, p2p_counters(c), p.tile, 0, 0, 0, 0)) return 1;
         EFA_CUDA(cudaEventRecord(c->ev_t1, c->compute_stream));
-        if (p2p_tile(c, p, r.w, O_all, 0, &r.launches)) return 1;
+        if (p2p_launch(c, p, r.w, O_all, &r.launches)) return 1;
         if (r.residual) {
             // the persistent kernel ends when every row block of this rank's output has been written
             r.launches++;
@@ -376,43 +403,48 @@ int run_stream(Run& r, char* output, efa_run_stats* st)
 
     EFA_CUDA(cudaMemsetAsync(counters, 0, (size_t)p.num_tiles * sizeof(int), c->compute_stream));
     EFA_CUDA(cudaEventRecord(reset_done, c->compute_stream));
-    // EFA_RESERVE_SMS = k runs the attention kernel in its persistent form on (SMs - k) CTAs, so that the
-    // projection and the AllReduce of finished tiles always find an SM. Measured on 8xB200 (benchmark
+    // p.reserve_sms = k runs the attention kernel in its persistent form on (SMs - k) CTAs, so that the
+    // projection and the reduction of finished tiles always find an SM. Measured on 8 GPUs (benchmark
     // shape) this loses: the projection of a group is then confined to the k reserved SMs, while with the
     // plain grid its CTAs (higher stream priority) spread over every SM an attention CTA retires from.
-    // Default off.
-    int reserve = 0;
-    if (const char* e = getenv("EFA_RESERVE_SMS")) reserve = atoi(e);
     EFA_CUDA(cudaEventRecord(c->ev_t0, c->compute_stream));
-    if (r.attention_raw(O_all, p.S, 0, p.S, c->compute_stream, counters, p.tile, reserve, band_rows)) return 1;
+    if (r.attention_raw(O_all, p.S, 0, p.S, c->compute_stream, counters, p.tile, p.reserve_sms, band_rows, 0, descending)) return 1;
     EFA_CUDA(cudaEventRecord(c->ev_t1, c->compute_stream));
 
     EFA_CUDA(cudaStreamWaitEvent(c->proj_stream, reset_done, 0));   // never observe a stale counter
-    // Tiles are signalled one by one; the projection and the AllReduce are launched once per group of
+    // Tiles are signalled one by one; the projection and the reduction are launched once per group of
     // consecutive tiles, after a front-end wait on every counter of the group. group_tiles = 1 is the
     // reference's schedule. Small tiles make one launch and one collective per tile cost more than the
     // attention of the tile (a 128-row tile of the benchmark shape is a few microseconds of attention on
     // eight GPUs), so the default groups about S/8 rows.
-    // Automatic grouping: S/8 rows per group, except that the last eighth of the rows is cut into
-    // S/16, S/32 and S/32: what is still exposed after the attention kernel ends is the projection and
-    // the collective of the last group, so that one should be small.
+    // From here on an error must not leave front-end waits behind on the projection stream: `fail` releases them.
+    auto fail = [&]() {
+        cudaStream_t rescue;
+        if (cudaStreamCreateWithFlags(&rescue, cudaStreamNonBlocking) == cudaSuccess) {
+            cudaMemsetAsync(counters, 0x7f, (size_t)p.num_tiles * sizeof(int), rescue);
+            cudaStreamSynchronize(rescue);
+            cudaStreamDestroy(rescue);
+        }
+        cudaStreamSynchronize(c->proj_stream);
+        return 1;
+    };
     for (int gidx = 0; gidx < ngroups; gidx++) {
         const int t0g = groups[gidx].first_tile, nt = groups[gidx].ntiles;
         for (int t = t0g; t < t0g + nt; t++)
-            EFA_CU(api->cuStreamWaitValue32((CUstream)c->proj_stream, (CUdeviceptr)(counters + t),
-                                            (cuuint32_t)target, CU_STREAM_WAIT_VALUE_GEQ));
+            if (check_cu(api->cuStreamWaitValue32((CUstream)c->proj_stream, (CUdeviceptr)(counters + t), (cuuint32_t)target,
+                                                  CU_STREAM_WAIT_VALUE_GEQ), "cuStreamWaitValue32", __FILE__, __LINE__)) return fail();
         const int rows = nt * p.tile;
         __half* O_t = O_all + (size_t)t0g * p.tile * p.d_local;
-        char* S_t = send_buf + (size_t)t0g * p.tile * r.row_bytes();
-        if (trace) EFA_CUDA(cudaEventRecord(c->trace_events[3 * gidx], c->proj_stream));
-        if (r.combine(O_t, p.S, t0g * p.tile, rows, c->proj_stream)) return 1;
-        if (r.project(O_t, S_t, rows)) return 1;
-        EFA_CUDA(cudaEventRecord(c->events[gidx], c->proj_stream));
-        if (trace) EFA_CUDA(cudaEventRecord(c->trace_events[3 * gidx + 1], c->proj_stream));
+        char* S_t = send_buf + (size_t)t0g * p.tile * r.send_row_bytes();
+        if (trace) cudaEventRecord(c->trace_events[3 * gidx], c->proj_stream);
+        if (r.combine(O_t, p.S, t0g * p.tile, rows, c->proj_stream)) return fail();
+        if (r.project(O_t, S_t, rows)) return fail();
+        if (cudaEventRecord(c->events[gidx], c->proj_stream) != cudaSuccess) return fail();
+        if (trace) cudaEventRecord(c->trace_events[3 * gidx + 1], c->proj_stream);
         const int slot = gidx % c->ncomm;
-        EFA_CUDA(cudaStreamWaitEvent(c->comm_streams[slot], c->events[gidx], 0));
-        if (r.allreduce(slot, S_t, output + (size_t)t0g * p.tile * r.row_bytes(), (size_t)rows * p.d)) return 1;
-        if (trace) EFA_CUDA(cudaEventRecord(c->trace_events[3 * gidx + 2], c->comm_streams[slot]));
+        if (cudaStreamWaitEvent(c->comm_streams[slot], c->events[gidx], 0) != cudaSuccess) return fail();
+        if (r.allreduce(slot, S_t, output + (size_t)t0g * p.tile * r.row_bytes(), (size_t)rows * p.d)) return fail();
+        if (trace) cudaEventRecord(c->trace_events[3 * gidx + 2], c->comm_streams[slot]);
     }
     const double t_enqueued = now_ms() - t0;
     if (sync_stream(c, c->compute_stream, counters, p.num_tiles)) return 1;
@@ -439,13 +471,13 @@ int run_stream(Run& r, char* output, efa_run_stats* st)
 int run_comm_only(Run& r, char* output, efa_run_stats* st)
 {
     efa_ctx* c = r.c; const efa_params& p = r.p;
-    if (scratch(c, p, 0, p.S, 0, 0, 0)) return 1;
-    char* send_buf = static_cast<char*>(c->send_buf);
-    EFA_CUDA(cudaMemset(send_buf, 0, (size_t)p.S * r.row_bytes()));
+    if (scratch(c, r, 0, p.S, 0, 0, 0)) return 1;
+    char* send_buf = r.send_base();
+    EFA_CUDA(cudaMemset(send_buf, 0, (size_t)p.S * r.send_row_bytes()));
     if (world_barrier(c->world)) return 1;
     const double t0 = now_ms();
     for (int t = 0; t < p.num_tiles; t++)
-        if (r.allreduce(0, send_buf + (size_t)t * p.tile * r.row_bytes(), output + (size_t)t * p.tile * r.row_bytes(), (size_t)p.tile * p.d)) return 1;
+        if (r.allreduce(0, send_buf + (size_t)t * p.tile * r.send_row_bytes(), output + (size_t)t * p.tile * r.row_bytes(), (size_t)p.tile * p.d)) return 1;
     if (sync_stream(c, c->comm_streams[0], nullptr, 0)) return 1;
     return finish_timing(c, t0, st, false, false, r.launches);
 }
@@ -460,16 +492,19 @@ int run_stream_host_pipelined(efa_ctx* c, const uint16_t* Qh, const uint16_t* Kh
     if (!p.causal || p.skip_proj) { set_error("pipelined host path: causal mask and projection required"); return 2; }
     if (!c->h2d_stream) EFA_CUDA(cudaStreamCreateWithFlags(&c->h2d_stream, cudaStreamNonBlocking));
     if (!c->d2h_stream) EFA_CUDA(cudaStreamCreateWithFlags(&c->d2h_stream, cudaStreamNonBlocking));
-    // chunks of about S/8 rows, whole tiles
+    // Chunks of about S/8 rows, whole tiles, and every chunk boundary a multiple of 128 rows: the attention
+    // kernels load keys in stages of up to 128 rows, and a stage must never reach into rows of the next chunk,
+    // which are still on their way to the device.
     int ct = (p.S / 8) / p.tile; if (ct < 1) ct = 1;
+    while (((long)ct * p.tile) % 128 != 0) ct++;
     const int nchunk = (p.num_tiles + ct - 1) / ct;
-    if (scratch(c, p, p.S, p.S, p.num_tiles, p.S, (size_t)3 * nchunk + 2)) return 1;
     Run r{c, dev, p};
+    if (scratch(c, r, p.S, p.S, p.num_tiles, p.S, (size_t)3 * nchunk + 2)) return 1;
     __half* O_all = static_cast<__half*>(c->O_all);
-    char* send_buf = static_cast<char*>(c->send_buf);
+    char* send_buf = r.send_base();
     char* output = static_cast<char*>(dev_out);
     char* host_bytes = reinterpret_cast<char*>(host_out);
-    const size_t rb = r.row_bytes();
+    const size_t rb = r.row_bytes(), sb = r.send_row_bytes();
     int* counters = c->counters;
     const int target = efa_blocks_per_tile(&p);
     auto ev_in = [&](int i) { return c->events[3 * i]; };
@@ -506,14 +541,14 @@ int run_stream_host_pipelined(efa_ctx* c, const uint16_t* Qh, const uint16_t* Kh
         for (int t = t0c; t < t0c + nt; t++)
             EFA_CU(api->cuStreamWaitValue32((CUstream)c->proj_stream, (CUdeviceptr)(counters + t), (cuuint32_t)target, CU_STREAM_WAIT_VALUE_GEQ));
         if (r.combine(O_all + (size_t)row0 * p.d_local, p.S, row0, rows, c->proj_stream)) return 1;
-        if (r.project(O_all + (size_t)row0 * p.d_local, send_buf + (size_t)row0 * rb, rows)) return 1;
+        if (r.project(O_all + (size_t)row0 * p.d_local, send_buf + (size_t)row0 * sb, rows)) return 1;
         EFA_CUDA(cudaEventRecord(ev_proj(i), c->proj_stream));
         const int slot = i % c->ncomm;
         EFA_CUDA(cudaStreamWaitEvent(c->comm_streams[slot], ev_proj(i), 0));
         if (p.skip_comm) {
-            EFA_CUDA(cudaMemcpyAsync(output + (size_t)row0 * rb, send_buf + (size_t)row0 * rb, (size_t)rows * rb,
+            EFA_CUDA(cudaMemcpyAsync(output + (size_t)row0 * rb, send_buf + (size_t)row0 * sb, (size_t)rows * rb,
                                      cudaMemcpyDeviceToDevice, c->comm_streams[slot]));
-        } else if (r.allreduce(slot, send_buf + (size_t)row0 * rb, output + (size_t)row0 * rb, (size_t)rows * p.d)) return 1;
+        } else if (r.allreduce(slot, send_buf + (size_t)row0 * sb, output + (size_t)row0 * rb, (size_t)rows * p.d)) return 1;
         EFA_CUDA(cudaEventRecord(ev_ar(i), c->comm_streams[slot]));
         if (host_out) {
             EFA_CUDA(cudaStreamWaitEvent(c->d2h_stream, ev_ar(i), 0));
@@ -542,9 +577,17 @@ int run_mode_impl(efa_ctx* c, int mode, const efa_weights& w, void* output, cons
         set_error("run_mode: mode %s writes no block output to add a residual to", kModeNames[mode]);
         return 2;
     }
-    if (p.proj_f32 && (residual || p.reduce == EFA_REDUCE_P2P)) {
+    if (p.proj_f32 && (residual || p.reduce != EFA_REDUCE_NCCL)) {
         set_error("run_mode: fp32 partial sums (proj_f32) go with the NCCL reduction and without a residual");
         return 2;
+    }
+    if (p.reduce != EFA_REDUCE_NCCL && p.reduce != EFA_REDUCE_P2P && p.reduce != EFA_REDUCE_NVLS) {
+        set_error("run_mode: unknown reduction %d", p.reduce);
+        return 2;
+    }
+    if (p.reduce == EFA_REDUCE_NVLS && p.R > 1 && !p.skip_comm) {
+        const char* why = nullptr;
+        if (!nvls_supported(c, p, &why)) { set_error("%s", why); return 5; }
     }
     Run r{c, w, p};
     char* out = static_cast<char*>(output);

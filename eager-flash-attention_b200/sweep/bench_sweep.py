@@ -58,15 +58,18 @@ def suite_commands(name, ranks):
         base = ["--S", 32768, "--H", 32, "--d_h", 128, "--causal", "--tile", 128, "--ncomm", 4]
         cmds.append((base + ["--modes", "attn,megatron,stream"], {}))
         cmds.append((base + ["--modes", "stream", "--no_comm"], {}))
-        cmds.append((base + ["--modes", "stream", "--trials", 1, "--warmup", 1], {"EFA_TRACE": "1"}))
+        cmds.append((base + ["--modes", "stream", "--trials", 1, "--warmup", 1, "--trace"], {}))
         for gt in (16, 64, 128):
             cmds.append((base + ["--modes", "stream", "--group_tiles", gt], {}))
         for split in (2, 4):
             cmds.append((base + ["--modes", "stream", "--split", split], {}))
         for ctas in (4, 8, 16):
             cmds.append((base + ["--modes", "stream"], {"NCCL_MAX_CTAS": str(ctas)}))
-            cmds.append((base + ["--modes", "stream"], {"NCCL_MAX_CTAS": str(ctas), "EFA_RESERVE_SMS": str(2 * ctas)}))
-        cmds.append((base + ["--modes", "stream", "--reduce", "p2p"], {}))
+            cmds.append((base + ["--modes", "stream", "--reserve_sms", 2 * ctas], {"NCCL_MAX_CTAS": str(ctas)}))
+        for order in ("asc", "desc"):
+            cmds.append((base + ["--modes", "stream", "--order", order], {}))
+        for reduce in ("p2p", "nvls"):
+            cmds.append((base + ["--modes", "stream", "--reduce", reduce], {}))
     else:
         raise ValueError(f"unknown suite {name!r}")
     out = []
@@ -107,7 +110,7 @@ def main(argv=None):
             elif suite.strip() == "overlap":
                 print(f"# {' '.join(cmd)}", file=out, flush=True)
             r = subprocess.run(full, capture_output=True, text=True, env=dict(os.environ, **env))
-            if "EFA_TRACE" in env:
+            if "--trace" in cmd:
                 sys.stderr.write(r.stderr)
             if r.returncode != 0:
                 print(f"# FAILED ({r.returncode}): {' '.join(full)}\n# {r.stderr.strip()[-300:]}", file=sys.stderr)

@@ -22,7 +22,7 @@
 extern "C" {
 #endif
 
-#define EFA_ABI_VERSION 2
+#define EFA_ABI_VERSION 3
 
 /* Element types of O / output buffers. */
 #define EFA_F32 0
@@ -133,8 +133,17 @@ enum {
 const char* efa_mode_name(int mode);     /* mode_name  (run_drivers.cuh:19) */
 int         efa_parse_mode(const char* s); /* parse_mode (run_drivers.cuh:20), -1 if unknown */
 
-/* How the per-tile partial sums are reduced across ranks. */
-enum { EFA_REDUCE_NCCL = 0, EFA_REDUCE_P2P = 1 };
+/* How the per-tile partial sums are reduced across ranks (allreduce, run_drivers.cu:26-30).
+ *   NCCL: ncclAllReduce on communicator t % ncomm as the reference does; fp16 on the wire with two ranks, the fp32
+ *         accumulators with more (NCCL adds fp16 in fp16, one rounding per hop), rounded once into the fp16 output.
+ *   P2P:  stream mode only: one persistent kernel does projection and reduction over peer-mapped memory.
+ *   NVLS: the NVSwitch sums the ranks' fp16 partial sums (fp32 accumulation, one rounding) through an NVLink
+ *         multicast object; one small kernel per reduction on the communication stream. Needs a device and fabric
+ *         with multicast support; otherwise the call fails with a message (nothing falls back silently). */
+enum { EFA_REDUCE_NCCL = 0, EFA_REDUCE_P2P = 1, EFA_REDUCE_NVLS = 2 };
+
+/* Order in which stream mode takes the rows of a causal problem (row_order). */
+enum { EFA_ROWS_AUTO = 0, EFA_ROWS_ASCENDING = 1, EFA_ROWS_DESCENDING = 2 };
 
 /* Derived problem description: AttnParams (attn_defs.cuh:70-84) without the fields of the
  * removed legacy kernel (B_M, B_N, kernel, flash). */
@@ -153,6 +162,17 @@ typedef struct efa_params {
                                    reference's types (attn_main.cu:262-273, run_drivers.cu:26-30), whose own --proj switch
                                    chose fp32 or tf32 math (attn_bench.cu:55,113-117). Operands stay fp16 either way.
                                    NCCL reduction only; not with a residual or the host-buffer entry point. */
+    int row_order;              /* stream mode: EFA_ROWS_ASCENDING = tiles complete first to last, the reference's order
+                                   (flash_attn_tc.cu:100-103). EFA_ROWS_DESCENDING = last rows first: under a causal mask the
+                                   last rows sweep the most keys, so the launch then ends on its shortest work items and
+                                   the consumer waits for the tiles in that same order. AUTO = descending when causal. */
+    int reduce_ctas;            /* thread blocks of the persistent kernel (P2P), 0 = chosen from the FLOP shares */
+    int band_rows;              /* stream mode: rows within which the attention kernel may take its work head by head
+                                   instead of in strict row order (K/V reuse in L2); 0 = chosen by efa_stream_plan,
+                                   -1 = strict row order */
+    int reserve_sms;            /* stream mode, diagnostics: > 0 runs the attention kernel in its persistent form and
+                                   leaves that many SMs without an attention CTA */
+    int trace;                  /* stream mode, diagnostics: 1 prints the timeline of the groups on stderr */
     efa_flash_params flash_tc;
 } efa_params;
 
@@ -163,16 +183,18 @@ const char* efa_attn_check_params(const efa_params* p);
 /* blocks_per_tile (attn_main.cuh:68, attn_main.cu:275-280): the counter target of a tile. */
 int efa_blocks_per_tile(const efa_params* p);
 
-/* The launch plan of stream mode with the NCCL reduction (the loop of run_stream, run_drivers.cu:227-240,
- * which there is one tile per iteration): consecutive tiles [first_tile, first_tile + ntiles) share one
- * projection launch and one AllReduce after a cuStreamWaitValue32 on each of their counters.
+/* The launch plan of stream mode (the loop of run_stream, run_drivers.cu:227-240, which there is one tile per
+ * iteration): consecutive tiles [first_tile, first_tile + ntiles) share one projection launch and one reduction
+ * after a cuStreamWaitValue32 on each of their counters. Groups are returned in the order in which they are
+ * waited for: first to last rows, or (*descending = 1) last to first.
  * group_tiles > 0: groups of that many tiles (1 = the reference's schedule). group_tiles == 0: about S/8
- * rows per group and the last eighth cut into S/16, S/32, S/32, so that what remains after the attention
- * kernel ends is small. *band_rows (if not NULL): the band within which the attention kernel may take its
- * work head by head instead of in strict row order, 0 = strict order. Host arithmetic only.
+ * rows per group and the eighth that completes last cut into S/16, S/32, S/32, so that what remains after the
+ * attention kernel ends is small. *band_rows (if not NULL): the band within which the attention kernel may take
+ * its work head by head instead of in strict row order, 0 = strict order: bands are used when the K and V of all
+ * local heads exceed what the L2 holds, and never exceed the smallest group. Host arithmetic only.
  * Returns the number of groups (groups may be NULL to count them), -1 on error. */
 typedef struct efa_stream_group { int first_tile, ntiles; } efa_stream_group;
-int efa_stream_plan(const efa_params* p, efa_stream_group* groups, int capacity, int* band_rows);
+int efa_stream_plan(const efa_params* p, efa_stream_group* groups, int capacity, int* band_rows, int* descending);
 
 /* Host control plane of one rank. The reference uses MPI for exactly these four operations
  * (MPI_Barrier / MPI_Allreduce(MAX) / MPI_Bcast / and, new here, an all-gather of opaque bytes for
@@ -201,6 +223,13 @@ typedef struct efa_ctx efa_ctx;   /* RunCtx (attn_defs.cuh:86-99): streams, comm
  * `prioritize`), ncomm NCCL communicators over the world's ranks. Collective over the world. */
 int efa_make_ctx(efa_ctx** out, const efa_world* world, int ncomm, int prioritize);
 int efa_destroy_ctx(efa_ctx* ctx);
+
+/* Limits of the waits that guard against a signal that never comes (the reference has none: a wrong counter
+ * target blocks its cuStreamWaitValue32 forever, run_drivers.cu:228-230). device_ms: how long a kernel of this
+ * context polls a tile counter, a peer's arrival flag or a barrier flag before it records a status
+ * (efa_kernel_status) and returns; default 10 s. host_ms: how long efa_run_mode waits for a stream before it
+ * releases the pending counter waits and returns an error; default 120 s. A value <= 0 leaves a limit as it is. */
+int efa_ctx_set_wait_limit_ms(efa_ctx* ctx, double device_ms, double host_ms);
 
 /* Device tensors of one rank: Weights (attn_main.cuh:7-12) for the fp16 data path. */
 typedef struct efa_weights {

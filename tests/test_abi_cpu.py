@@ -25,7 +25,7 @@ def test_library_exports_every_declared_symbol(pkg):
 
 
 def test_abi_version(pkg):
-    assert pkg.lib().efa_abi_version() == 2
+    assert pkg.lib().efa_abi_version() == 3
 
 
 def test_mode_names_round_trip(pkg):
@@ -80,9 +80,10 @@ def test_compute_entry_points_fail_loudly_without_a_device(pkg):
         pkg.make_ctx(pkg.World())
 
 
-def _plan(pkg, S, d, H, tile, group_tiles=0, R=1):
-    p = pkg.make_params(S, d, H, tile, causal=1, world_size=R)
+def _plan(pkg, S, d, H, tile, group_tiles=0, R=1, causal=1, order=0):
+    p = pkg.make_params(S, d, H, tile, causal=causal, world_size=R)
     p.group_tiles = group_tiles
+    p.row_order = order
     return p, *pkg.stream_plan(p)
 
 
@@ -90,38 +91,55 @@ def test_stream_plan_covers_every_tile_once(pkg):
     # stream mode waits on every tile's counter exactly once, whatever the grouping (run_drivers.cu:227-240)
     for S, tile, gt in [(4096, 128, 0), (4096, 128, 1), (4096, 128, 5), (32768, 128, 0), (65536, 64, 0),
                         (65536, 256, 7), (1024, 256, 0), (256, 256, 0), (8192, 64, 1000)]:
-        p, groups, band = _plan(pkg, S, 1024, 16, tile, gt)
-        covered = [t for first, n in groups for t in range(first, first + n)]
-        assert covered == list(range(p.num_tiles)), (S, tile, gt)
-        assert all(n >= 1 for _, n in groups)
-        assert band % 256 == 0 and (band == 0 or 512 <= band <= 2048)
+        for causal, order in [(0, 0), (1, 0), (1, 1), (0, 2)]:
+            p, groups, band, desc = _plan(pkg, S, 1024, 16, tile, gt, causal=causal, order=order)
+            assert desc == (order == 2 or (order == 0 and causal == 1))
+            covered = sorted(t for first, n in groups for t in range(first, first + n))
+            assert covered == list(range(p.num_tiles)), (S, tile, gt)
+            assert all(n >= 1 for _, n in groups)
+            firsts = [first for first, _ in groups]
+            assert firsts == sorted(firsts, reverse=desc)          # waited for in the order they complete
+            assert band % 256 == 0 and (band == 0 or 512 <= band <= 2048)
 
 
 def test_stream_plan_per_tile_schedule_is_the_reference_one(pkg):
-    p, groups, band = _plan(pkg, 4096, 1024, 16, 128, group_tiles=1)
-    assert groups == [(t, 1) for t in range(32)]
+    p, groups, band, desc = _plan(pkg, 4096, 1024, 16, 128, group_tiles=1, order=1)
+    assert groups == [(t, 1) for t in range(32)] and not desc
     assert band == 0                       # strict row order: a tile's rows complete before the next tile's
 
 
-def test_stream_plan_automatic_grouping_tapers_the_last_eighth(pkg):
-    # benchmark shape: S/8 rows per group, then S/16, S/32, S/32; bands of S/16 rows
-    p, groups, band = _plan(pkg, 32768, 4096, 32, 128, R=8)
-    assert [n for _, n in groups] == [32] * 7 + [16, 8, 8]
+def test_stream_plan_automatic_grouping_tapers_the_eighth_that_completes_last(pkg):
+    # benchmark shape on one rank: S/8 rows per group, then S/16, S/32, S/32; K and V of 32 heads (512 MB) exceed
+    # the L2, so the attention kernel works in bands of S/16 rows
+    p, groups, band, desc = _plan(pkg, 32768, 4096, 32, 128, R=1, order=1)
+    assert [n for _, n in groups] == [32] * 7 + [16, 8, 8] and groups[0] == (0, 32)
     assert band == 2048
     # a band never exceeds the smallest group it has to complete within... except by design the two S/32 groups
     assert band <= 2 * min(n for _, n in groups) * 128
+    # the same shape, last rows first (the default under a causal mask): the small groups are the FIRST rows
+    p, groups, band, desc = _plan(pkg, 32768, 4096, 32, 128, R=1)
+    assert desc and [n for _, n in groups] == [32] * 7 + [16, 8, 8]
+    assert groups[0] == (224, 32) and groups[-1] == (0, 8) and groups[-2] == (8, 8)
+    # eight ranks: four heads' K and V (64 MB) stay in the L2, strict row order
+    p, groups, band, desc = _plan(pkg, 32768, 4096, 32, 128, R=8)
+    assert band == 0
     # explicit grouping: the band is the group
-    p, groups, band = _plan(pkg, 32768, 4096, 32, 128, group_tiles=8)
+    p, groups, band, desc = _plan(pkg, 32768, 4096, 32, 128, group_tiles=8)
     assert [n for _, n in groups] == [8] * 32 and band == 1024
+    # an explicit band, and none
+    p.band_rows = 512
+    assert pkg.stream_plan(p)[1] == 512
+    p.band_rows = -1
+    assert pkg.stream_plan(p)[1] == 0
     # small problems: one tile per group when S/8 is below a tile
-    p, groups, band = _plan(pkg, 512, 1024, 16, 128)
+    p, groups, band, desc = _plan(pkg, 512, 1024, 16, 128)
     assert [n for _, n in groups] == [1, 1, 1, 1] and band == 0
 
 
 def test_stream_plan_counts_without_a_buffer_and_rejects_a_short_one(pkg):
     import ctypes as C
     p = pkg.make_params(32768, 4096, 32, 128, causal=1, world_size=1)
-    assert pkg.lib().efa_stream_plan(C.byref(p), None, 0, None) == 10
+    assert pkg.lib().efa_stream_plan(C.byref(p), None, 0, None, None) == 10
     buf = (pkg.StreamGroup * 4)()
-    assert pkg.lib().efa_stream_plan(C.byref(p), buf, 4, None) == -1
+    assert pkg.lib().efa_stream_plan(C.byref(p), buf, 4, None, None) == -1
     assert "groups" in pkg.last_error()

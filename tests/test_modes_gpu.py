@@ -94,7 +94,10 @@ def test_single_gpu_benchmark_configuration(pkg, oracle, torch_cuda, ctx, causal
         assert_close(oracle, got[rows], ref, name)
 
 
-@pytest.mark.parametrize("shape", [(512, 256, 4, 128, 1), (512, 256, 4, 128, 2), (2048, 512, 4, 128, 4), (2048, 1024, 8, 256, 1)],
+@pytest.mark.parametrize("shape", [(512, 256, 4, 128, 1), (512, 256, 4, 128, 2), (2048, 512, 4, 128, 4), (2048, 1024, 8, 256, 1),
+                                   # 64-row tiles: S/8 rows per chunk would be 64 or 192 rows, which the chunking rounds to
+                                   # multiples of 128 so that no key stage reaches into rows still being copied in
+                                   (512, 256, 4, 64, 1), (1536, 512, 4, 64, 1), (1536, 256, 8, 64, 1)],
                          ids=lambda c: "S%d_d%d_H%d_t%d_s%d" % c)
 def test_host_buffer_entry_point(pkg, oracle, torch_cuda, ctx, shape):
     """Stream mode on pinned host buffers: copy-in, compute and copy-out pipelined over row chunks; with
@@ -141,14 +144,13 @@ def test_stream_mode_with_the_fused_projection_kernel_single_rank(pkg, oracle, t
 
 @pytest.mark.parametrize("case", [(1024, 512, 8, 128, 1, 1), (2048, 1024, 8, 256, 0, 1), (4096, 1024, 16, 128, 1, 1), (2048, 512, 8, 128, 1, 2)],
                          ids=lambda c: "S%d_d%d_H%d_t%d_c%d_s%d" % c)
-def test_stream_mode_with_reserved_sms(pkg, oracle, torch_cuda, ctx, case, monkeypatch):
-    """The persistent form of the attention kernel (used with more than one rank): fewer CTAs than SMs,
-    work items taken from a global counter in row order, barriers rebuilt per item. EFA_RESERVE_SMS forces
-    it on one rank; 100 reserved SMs leave 48 CTAs, so every CTA processes several items."""
+def test_stream_mode_with_reserved_sms(pkg, oracle, torch_cuda, ctx, case):
+    """The persistent form of the attention kernel: fewer CTAs than SMs, work items taken from a global counter,
+    barriers rebuilt per item. 100 reserved SMs leave 48 CTAs, so every CTA processes several items."""
     torch = torch_cuda
     S, d, H, tile, causal, split = case
-    monkeypatch.setenv("EFA_RESERVE_SMS", "100")
     p = pkg.make_params(S, d, H, tile, 2, split, causal)
+    p.reserve_sms = 100
     bits, vals = ref_inputs_f16(oracle, S, d, H, 1, 0, 42) if S <= 2048 else normal_inputs_f16(pkg, oracle, p, 0, 42)
     rows = None if S <= 2048 else np.arange(0, S, 13, dtype=np.int32)
     ref = oracle.block_rows([vals], d, causal, rows)

@@ -65,6 +65,7 @@ def test_overlap_suite_names_its_environment():
                        capture_output=True, text=True)
     assert r.returncode == 0, r.stderr
     lines = [l for l in r.stdout.splitlines() if "attn_bench" in l]
-    assert any(l.startswith("EFA_TRACE=1 ") for l in lines)
-    assert any(l.startswith("NCCL_MAX_CTAS=8 EFA_RESERVE_SMS=16 ") for l in lines)
+    assert any("--trace" in l for l in lines)
+    assert any(l.startswith("NCCL_MAX_CTAS=8 ") and "--reserve_sms 16" in l for l in lines)
     assert any("--no_comm" in l for l in lines) and any("--split 4" in l for l in lines) and any("--reduce p2p" in l for l in lines)
+    assert any("--reduce nvls" in l for l in lines) and any("--order desc" in l for l in lines)
