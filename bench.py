@@ -10,7 +10,11 @@ sharded over the N ranks (strong scaling: the global problem is fixed). Rank 0 p
 `value` is the block time with the fp16 inputs resident in HBM; `e2e` is the same block through the
 host-buffer entry point (pinned host Q/K/V/W_O copied in, fp16 result copied out, every step).
 `--impl reference` times the unmodified reference programs built under oracle/_ref (its own CUDA
-build; the reference has no CPU implementation), or says why it cannot.
+build; the reference has no CPU implementation), or says why it cannot: at this workload's tile and ncomm,
+and at its own best tile (the tiles and split of its sweep script).
+
+Every time in the line is the mean over the timed steps of the same per-step figure (one statistic
+throughout): `value`, `modes_ms` and `roofline.attn_kernel_ms` can be compared with one another.
 """
 import argparse
 import json
@@ -25,6 +29,16 @@ sys.path.insert(0, ROOT)
 
 WORKLOAD = dict(S=32768, H=32, d_h=128, causal=1, tile=128, ncomm=4, split=1, nbuf=2)
 METRIC = "ms per TP attention block (attn+W_o+AllReduce)"
+NVLINK_GBS = 900.0      # per direction and GPU, nominal: the link bound the block roofline is taken against
+
+# --reduce auto: the reduction that measured fastest for this workload at each rank count (stream mode, ms per
+# block on B200s of one NVSwitch box; the table these figures come from is in the design notes). One rank
+# reduces nothing; "nvls" needs NVLink multicast and is only chosen where efa reports it usable.
+REDUCE_BY_RANKS = {1: "nccl", 2: "nccl", 4: "nccl", 8: "nccl"}
+
+# DRAM bytes (read + written) of one attention launch of the benchmark shape with all 32 heads on one GPU, by
+# (mode, rows taken last-first): ncu captures, one launch each.
+ATTN_TRAFFIC_32_HEADS = {("stream", False): 5.105e9}
 
 
 def measured_peaks():
@@ -127,30 +141,50 @@ def run_reference(args, world_size, rank):
     launch = os.path.join(ROOT, "oracle", "_ref", "efa_launch")
     if not (os.path.exists(exe) and os.path.exists(launch)):
         return dict(impl="reference", unavailable="oracle/_ref/attn_bench is not built (run __graft_entry__.build() where the reference sources are mounted)")
-    cmd = [launch, "-n", str(world_size), exe, "--S", str(W["S"]), "--H", str(W["H"]), "--d_h", str(W["d_h"]),
-           "--tile", str(W["tile"]), "--ncomm", str(W["ncomm"]), "--causal", "--modes", "attn,megatron,stream",
-           "--warmup", str(args.warmup), "--trials", str(args.steps)]
     env = dict(os.environ)
     for k in ("RANK", "LOCAL_RANK", "WORLD_SIZE", "MASTER_ADDR", "MASTER_PORT"):
         env.pop(k, None)
-    try:
-        r = subprocess.run(cmd, capture_output=True, text=True, timeout=1500, env=env)
-    except subprocess.TimeoutExpired:
-        return dict(impl="reference", unavailable="the reference attn_bench did not finish within 1500 s")
-    if r.returncode != 0:
-        return dict(impl="reference", unavailable="reference attn_bench exited %d: %s" % (r.returncode, r.stderr.strip().splitlines()[-1:] or ""))
-    rows = {}
-    for line in r.stdout.splitlines():
-        f = line.split(",")
-        if len(f) >= 17 and f[0].isdigit():
-            rows[f[11]] = dict(min=float(f[12]), max=float(f[13]), mean=float(f[14]), median=float(f[15]), std=float(f[16]))
+
+    def run(tile, ncomm, split, modes, warmup, trials):
+        cmd = [launch, "-n", str(world_size), exe, "--S", str(W["S"]), "--H", str(W["H"]), "--d_h", str(W["d_h"]),
+               "--tile", str(tile), "--ncomm", str(ncomm), "--split", str(split), "--causal", "--modes", modes,
+               "--warmup", str(warmup), "--trials", str(trials)]
+        try:
+            r = subprocess.run(cmd, capture_output=True, text=True, timeout=1500, env=env)
+        except subprocess.TimeoutExpired:
+            return None, "the reference attn_bench did not finish within 1500 s"
+        if r.returncode != 0:
+            return None, "reference attn_bench exited %d: %s" % (r.returncode, r.stderr.strip().splitlines()[-1:] or "")
+        rows = {}
+        for line in r.stdout.splitlines():
+            f = line.split(",")
+            if len(f) >= 17 and f[0].isdigit():
+                rows[f[11]] = dict(min=float(f[12]), max=float(f[13]), mean=float(f[14]), median=float(f[15]), std=float(f[16]))
+        return rows, None
+
+    rows, why = run(W["tile"], W["ncomm"], W["split"], "attn,megatron,stream", args.warmup, args.steps)
+    if rows is None:
+        return dict(impl="reference", unavailable=why)
     if args.mode not in rows:
         return dict(impl="reference", unavailable="no %s row in the reference's output" % args.mode)
-    ms = rows[args.mode]["median"]
+    ms = rows[args.mode]["mean"]
+    # The reference at its own best: the tiles and split-KV factor its sweep script uses (S/32 ... S/8, --split 4,
+    # eight communicators), fewer trials each. Reported beside the like-for-like figure, not in place of it.
+    best = None
+    sweep = {}
+    for tile in (1024, 2048, 4096):
+        r2, _ = run(tile, 8, 4, "stream", 2, max(3, min(args.steps, 5)))
+        if r2 and "stream" in r2:
+            sweep["tile=%d split=4 ncomm=8" % tile] = r2["stream"]["mean"]
+    if sweep:
+        k = min(sweep, key=sweep.get)
+        best = dict(stream_ms=sweep[k], config=k, all=sweep)
     base.update(value=ms, ms_per_step=ms, tokens_per_s=W["S"] / (ms * 1e-3),
-                modes={k: v["median"] for k, v in rows.items()},
+                modes_ms={k: v["mean"] for k, v in rows.items()},
+                best_of_its_own_sweep=best,
+                best_ms=min([ms, rows.get("megatron", {}).get("mean", ms)] + ([best["stream_ms"]] if best else [])),
                 cpu_baseline=dict(value=ms, unit="ms", cores=0, kind="reference",
-                                  sample="the reference's own CUDA programs (it has no CPU implementation); whole workload, median of the timed trials"),
+                                  sample="the reference's own CUDA programs (it has no CPU implementation); whole workload, mean of the timed trials"),
                 e2e=dict(value=ms, unit="ms", h2d_bytes_per_step=0, d2h_bytes_per_step=0),
                 gpu_launches=None)
     return base
@@ -163,9 +197,15 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--mode", default="stream", choices=["stream", "megatron"])
-    ap.add_argument("--reduce", default="auto", choices=["auto", "nccl", "p2p"],
-                    help="stream mode: per-group NCCL AllReduce, or the persistent projection+reduction kernel over "
-                         "peer memory; auto = whichever measured faster for this rank count")
+    ap.add_argument("--reduce", default="auto", choices=["auto", "nccl", "p2p", "nvls"],
+                    help="how the partial sums are reduced: NCCL AllReduce per group of tiles, the persistent "
+                         "projection+reduction kernel over peer memory (stream mode), or the NVSwitch through an NVLink "
+                         "multicast object; auto = the one that measured fastest for this rank count")
+    ap.add_argument("--wire", default="auto", choices=["auto", "f16", "f32"],
+                    help="element type of the partial sums on the links: the fp32 accumulators (auto), or fp16 (half the bytes, "
+                         "one more rounding per partial sum)")
+    ap.add_argument("--order", default="auto", choices=["auto", "asc", "desc"],
+                    help="stream mode: order in which the rows are taken and waited for (auto = last rows first under a causal mask)")
     ap.add_argument("--group-tiles", type=int, default=0, help="tiles per projection + AllReduce launch (0 = auto, 1 = per tile)")
     ap.add_argument("--split", type=int, default=0,
                     help="split-KV factor of the attention kernel (the reference's --split); 0 = the value chosen for this rank count")
@@ -211,12 +251,13 @@ def main():
     if why:
         raise SystemExit(f"invalid workload for {world_size} ranks: {why}")
     if args.reduce == "auto":
-        # Measured on 1, 2, 4 and 8 B200s for this workload: grouped NCCL AllReduces are as fast as or faster
-        # than the fused peer-memory kernel at every rank count (profiles/stream_modes_C5.md has the table).
-        args.reduce = "nccl"
-    p.reduce = pkg.REDUCE_P2P if args.reduce == "p2p" else pkg.REDUCE_NCCL
+        args.reduce = REDUCE_BY_RANKS.get(world_size, "nccl")
+    p.reduce = dict(nccl=pkg.REDUCE_NCCL, p2p=pkg.REDUCE_P2P, nvls=pkg.REDUCE_NVLS)[args.reduce]
+    p.row_order = dict(auto=pkg.ROWS_AUTO, asc=pkg.ROWS_ASCENDING, desc=pkg.ROWS_DESCENDING)[args.order]
+    p.wire = dict(auto=pkg.WIRE_AUTO, f16=pkg.WIRE_F16, f32=pkg.WIRE_F32)[args.wire]
     p.group_tiles = args.group_tiles
     mode = pkg.parse_mode(args.mode)
+    descending = bool(pkg.stream_plan(p)[2])
 
     # Synthetic inputs in pinned host memory (N(0,1) Q/K/V, W_O ~ N(0, 1/d)), then resident copies.
     qkv_shape = (p.H_local, p.S, p.d_h)
@@ -226,10 +267,17 @@ def main():
     host_out = torch.empty((p.S, p.d), dtype=torch.float16).pin_memory() if rank == 0 else None
     pkg.fill_host_inputs(p, rank, 42, pkg.RECIPE_NORMAL, *host)
     dev = [h.cuda() for h in host]
-    out = torch.zeros((p.S, p.d), dtype=torch.float16, device="cuda")
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")      # > 126 MB L2
     weights = pkg.Weights(*(t.data_ptr() for t in dev))
     ctx = pkg.make_ctx(world, ncomm=W["ncomm"])
+    if args.reduce == "nvls" and world_size > 1:
+        # the multicast reduction writes its result in place into the context's symmetric region
+        class _Region:
+            def __init__(self, ptr, shape):
+                self.__cuda_array_interface__ = dict(shape=shape, typestr="<f2", data=(ptr, False), version=2)
+        out = torch.as_tensor(_Region(pkg.nvls_output(ctx, p), (p.S, p.d)), device="cuda")
+    else:
+        out = torch.zeros((p.S, p.d), dtype=torch.float16, device="cuda")
 
     def barrier():
         torch.cuda.synchronize()
@@ -258,37 +306,43 @@ def main():
         raise SystemExit(f"rank {rank}: a kernel reported status {status}")
     wall = [s.wall_ms for s in stats]           # each already the max over ranks
     ms = statistics.mean(wall)
-    attn_ms = statistics.median([s.attn_kernel_ms for s in stats])
+    attn_ms = statistics.mean([s.attn_kernel_ms for s in stats])
     launches = stats[-1].kernel_launches
 
-    # other modes, for context (fewer steps)
-    modes = {args.mode: statistics.median(wall)}
-    for other in ("attn", "megatron", "stream"):
-        if other == args.mode:
-            continue
-        m = pkg.parse_mode(other)
+    def timed(m, output, steps):
+        """Mean block time of mode m over `steps` steps after two untimed ones."""
         ts = []
-        for i in range(2 + min(args.steps, 5)):
+        for i in range(2 + steps):
             flush.fill_(1)
             barrier()
-            st = pkg.run_mode(ctx, m, weights, out, p)
+            st = pkg.run_mode(ctx, m, weights, output, p)
             if i >= 2:
                 ts.append(st.wall_ms)
-        modes[other] = statistics.median(ts)
+        return statistics.mean(ts)
+
+    # other modes, for context (fewer steps)
+    few = min(args.steps, 5)
+    modes = {args.mode: ms}
+    for other in ("attn", "megatron", "stream"):
+        if other != args.mode:
+            modes[other] = timed(pkg.parse_mode(other), out, few)
+    # the same modes with the reference's types (fp32 partial sums, fp32 reduction, fp32 output): the like-for-like
+    # precision figure beside the reference arm
+    modes_f32 = {}
+    out32 = torch.zeros((p.S, p.d), dtype=torch.float32, device="cuda")
+    saved_reduce = p.reduce
+    p.proj_f32, p.reduce = 1, pkg.REDUCE_NCCL
+    for other in ("megatron", "stream"):
+        modes_f32[other] = timed(pkg.parse_mode(other), out32, few)
+    p.proj_f32, p.reduce = 0, saved_reduce
+    del out32
     # exposed communication: (T - T(--no_comm)) / T with the reference's diagnostic flag
     exposed = None
     if world_size > 1:
         p.skip_comm = 1
-        ts = []
-        for i in range(2 + min(args.steps, 5)):
-            flush.fill_(1)
-            barrier()
-            st = pkg.run_mode(ctx, mode, weights, out, p)
-            if i >= 2:
-                ts.append(st.wall_ms)
+        t_nc = timed(mode, out, few)
         p.skip_comm = 0
-        t_nc = statistics.median(ts)
-        exposed = max(0.0, (statistics.median(wall) - t_nc) / statistics.median(wall))
+        exposed = max(0.0, (ms - t_nc) / ms)
 
     # end to end through the host-buffer entry point
     for _ in range(2):
@@ -302,7 +356,7 @@ def main():
     achieved = fl / (attn_ms * 1e-3) / 1e12 if attn_ms > 0 else 0.0
     proj_fl = 2.0 * p.S * p.d_local * p.d
     link_bytes = 2.0 * (world_size - 1) / world_size * p.S * p.d * 2
-    t_roof = max((fl + proj_fl) / (pk["tflops"] * 1e12), link_bytes / 770e9) * 1e3
+    t_roof = max((fl + proj_fl) / (pk["tflops"] * 1e12), link_bytes / (NVLINK_GBS * 1e9)) * 1e3
 
     line = None
     if rank == 0:
@@ -315,24 +369,26 @@ def main():
             ms_per_step=ms, higher_is_better=False, scaling="strong", vs_baseline=None, dtype="f16 (f32 accumulate)",
             data="synthetic",
             config=dict(workload=f"S={p.S} H={p.H} d_h={p.d_h} causal tile={p.tile} ncomm={W['ncomm']} TP={world_size}",
-                        mode=args.mode, split=p.split, reduce=args.reduce, group_tiles=args.group_tiles or "auto (S/8 rows per launch)",
+                        mode=args.mode, split=p.split, reduce=args.reduce, wire=args.wire, row_order=args.order,
+                        group_tiles=args.group_tiles or "auto (S/8 rows per launch)",
                         l2="256 MB buffer written between steps",
                         e2e="pinned host Q/K/V/W_O copied in by every rank, fp16 [S][d] result copied out by rank 0 (it is "
                             "identical on all ranks); copy-in, compute and copy-out pipelined over row chunks",
                         inputs="Q,K,V ~ N(0,1) fp16 [H_local][S][d_h]; W_O ~ N(0,1/d) fp16; seed 42"),
             tokens_per_s=p.S / (ms * 1e-3),
-            modes_ms=modes, exposed_comm_frac=exposed,
-            block_roofline=dict(t_ms=t_roof, frac=t_roof / ms, peak=f"{pk['tflops']} TFLOP/s bf16 {pk['source']}; 770 GB/s NVLink measured"),
+            modes_ms=modes, modes_ms_proj_f32=modes_f32, exposed_comm_frac=exposed,
+            block_roofline=dict(t_ms=t_roof, frac=t_roof / ms,
+                                peak=f"{pk['tflops']} TFLOP/s bf16 {pk['source']}; {NVLINK_GBS:.0f} GB/s per direction NVLink nominal"),
             roofline=dict(bound="tensor", kernel="fa_fwd_ws_kernel<128>", achieved=achieved, peak=pk["tflops"], unit="TFLOP/s",
                           frac=achieved / pk["tflops"], peak_source=f"of {pk['source']} (burst bf16)",
                           frac_sustained=achieved / pk["tflops_sustained"], attn_kernel_ms=attn_ms,
                           algorithmic_flops=fl,
-                          # dram__bytes_read.sum + dram__bytes_write.sum of this kernel's stream-mode launch at the
-                          # benchmark shape on one rank (32 heads): 4.797 GB + 0.308 GB, one ncu capture
-                          # (profiles/fa_fwd_ws_kernel_d128_S32768_traffic.md). Heads are independent, so a rank's
-                          # traffic is that figure times H_local / 32. Other shapes were not captured.
-                          traffic=(5.105e9 * p.H_local / 32 if (p.S == 32768 and p.d_h == 128 and p.causal and args.mode == "stream"
-                                                                and p.split == 1) else None),
+                          # dram__bytes_read.sum + dram__bytes_write.sum of this kernel's launch, from one ncu capture of
+                          # the benchmark shape on one rank (32 heads); heads are independent, so a rank's traffic is
+                          # that figure times H_local / 32. Shapes that were not captured report null.
+                          traffic=(ATTN_TRAFFIC_32_HEADS.get((args.mode, descending)) * p.H_local / 32
+                                   if (p.S == 32768 and p.d_h == 128 and p.causal and p.split == 1
+                                       and (args.mode, descending) in ATTN_TRAFFIC_32_HEADS) else None),
                           algorithmic_bytes=2.0 * p.S * p.d_local * 4),      # Q, K, V read once, O written once (fp16)
             cpu_baseline=cpu,
             e2e=dict(value=e2e_ms, unit="ms", h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h),

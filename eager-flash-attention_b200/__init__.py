@@ -20,13 +20,15 @@ import os
 from typing import Optional, Sequence
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libefa_b200.so")
+# EFA_B200_LIB names another build of the same library (a debug build, say); the default is the one beside this file.
+LIB_PATH = os.environ.get("EFA_B200_LIB") or os.path.join(_HERE, "libefa_b200.so")
 
 F32, F16 = 0, 1
 MODE_ATTN, MODE_ATTN_TILED, MODE_MEGATRON, MODE_SYNC, MODE_OVERLAP, MODE_STREAM, MODE_COMM = range(7)
 MODE_NAMES = ("attn", "attn_tiled", "megatron", "sync", "overlap", "stream", "comm")
 REDUCE_NCCL, REDUCE_P2P, REDUCE_NVLS = 0, 1, 2
 ROWS_AUTO, ROWS_ASCENDING, ROWS_DESCENDING = 0, 1, 2
+WIRE_AUTO, WIRE_F16, WIRE_F32 = 0, 1, 2
 RECIPE_REF, RECIPE_NORMAL = 0, 1
 
 
@@ -53,7 +55,7 @@ class Params(C.Structure):
                 ("nbuf", C.c_int), ("split", C.c_int), ("causal", C.c_int),
                 ("skip_proj", C.c_int), ("skip_comm", C.c_int), ("reduce", C.c_int), ("group_tiles", C.c_int),
                 ("proj_f32", C.c_int), ("row_order", C.c_int), ("reduce_ctas", C.c_int), ("band_rows", C.c_int),
-                ("reserve_sms", C.c_int), ("trace", C.c_int), ("flash_tc", FlashParams)]
+                ("reserve_sms", C.c_int), ("trace", C.c_int), ("wire", C.c_int), ("debug_target_bias", C.c_int), ("flash_tc", FlashParams)]
 
 
 _BARRIER_FN = C.CFUNCTYPE(C.c_int, C.c_void_p)
@@ -92,6 +94,7 @@ _SIGNATURES = {
                                             C.POINTER(FlashParams), C.c_void_p, C.c_void_p, C.c_int]),
     "efa_flash_attn_tc_forward_noalloc": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int,
                                                     C.c_int, C.c_int, C.POINTER(FlashParams), C.c_void_p]),
+    "efa_flash_attn_tc_noalloc_status": (C.c_int, [C.POINTER(C.c_int), C.c_int]),
     "efa_flash_attn_tc_combine": (C.c_int, [C.POINTER(FlashPartials), C.c_void_p, C.c_int, C.c_int, C.c_int,
                                             C.POINTER(FlashParams), C.c_void_p]),
     "efa_flash_attn_tc_check_params": (C.c_char_p, [C.POINTER(FlashParams), C.c_int]),
@@ -107,6 +110,7 @@ _SIGNATURES = {
     "efa_blocks_per_tile": (C.c_int, [C.POINTER(Params)]),
     "efa_stream_plan": (C.c_int, [C.POINTER(Params), C.POINTER(StreamGroup), C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "efa_ctx_set_wait_limit_ms": (C.c_int, [C.c_void_p, C.c_double, C.c_double]),
+    "efa_nvls_output": (C.c_int, [C.c_void_p, C.POINTER(Params), C.POINTER(C.c_void_p)]),
     "efa_world_selftest": (C.c_int, [C.POINTER(WorldStruct)]),
     "efa_make_ctx": (C.c_int, [C.POINTER(C.c_void_p), C.POINTER(WorldStruct), C.c_int, C.c_int]),
     "efa_destroy_ctx": (C.c_int, [C.c_void_p]),
@@ -244,6 +248,14 @@ def flash_attn_tc_forward_noalloc(Q, K, V, O, q_start: int, q_rows: int, fp: Fla
     _check(rc, "flash_attn_tc_forward_noalloc")
 
 
+def flash_attn_tc_noalloc_status(reset: bool = False) -> Sequence[int]:
+    """(code, block, site, 0) of the kernels launched by flash_attn_tc_forward_noalloc on the current device; code 0 =
+    none of them gave up a bounded wait. ``reset`` clears the word after reading."""
+    out = (C.c_int * 4)()
+    _check(lib().efa_flash_attn_tc_noalloc_status(out, int(bool(reset))), "flash_attn_tc_noalloc_status")
+    return tuple(out)
+
+
 def flash_attn_tc_combine(part: FlashPartials, O, row0: int, rows: int, fp: FlashParams, stream=None,
                           o_dtype: int = F16) -> None:
     """flash_attn_tc_combine (flash_attn_tc.cuh:54-57)."""
@@ -370,6 +382,14 @@ class Ctx:
 
 def make_ctx(world: World, ncomm: int = 1, prioritize: bool = True) -> Ctx:
     return Ctx(world, ncomm, prioritize)
+
+
+def nvls_output(ctx: Ctx, p: Params) -> int:
+    """Device address of an fp16 [S][d] output buffer inside the context's multicast region, which the NVLS reduction
+    writes in place (collective). Valid until the context is destroyed or the region grows."""
+    out = C.c_void_p()
+    _check(lib().efa_nvls_output(ctx.handle, C.byref(p), C.byref(out)), "nvls_output")
+    return int(out.value)
 
 
 def set_wait_limit_ms(ctx: Ctx, device_ms: float = 0.0, host_ms: float = 0.0) -> None:

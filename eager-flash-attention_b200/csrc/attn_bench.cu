@@ -97,7 +97,7 @@ static void usage(const char* prog)
         "          [--modes attn,attn_tiled,megatron,sync,overlap,stream,comm] [--no-header]\n"
         "          [--causal] [--proj fp16|fp32] [--no_prio] [--no_proj] [--no_comm]\n"
         "          [--reduce nccl|p2p|nvls] [--group_tiles 0] [--order auto|asc|desc] [--data normal|ref] [--seed 42] [--residual]\n"
-        "          [--band_rows 0] [--reserve_sms 0] [--reduce_ctas 0] [--trace]\n", prog);
+        "          [--wire auto|f16|f32] [--band_rows 0] [--reserve_sms 0] [--reduce_ctas 0] [--trace] [--own_output]\n", prog);
 }
 
 int main(int argc, char** argv)
@@ -112,7 +112,7 @@ int main(int argc, char** argv)
     const int device = g_rank % ndev;
     CUDA_OK(cudaSetDevice(device));
 
-    const CommandLine cl(argc, argv, {"--help", "--causal", "--no-header", "--no_prio", "--no_proj", "--no_comm", "--residual", "--trace"});
+    const CommandLine cl(argc, argv, {"--help", "--causal", "--no-header", "--no_prio", "--no_proj", "--no_comm", "--residual", "--trace", "--own_output"});
     if (cl.on("--help")) {
         if (g_rank == 0) usage(argv[0]);
         MPI_Finalize();
@@ -176,6 +176,10 @@ int main(int argc, char** argv)
     if (order_s == "asc") p.row_order = EFA_ROWS_ASCENDING;
     else if (order_s == "desc") p.row_order = EFA_ROWS_DESCENDING;
     else if (order_s != "auto") fail("--order must be auto, asc or desc");
+    const std::string wire_s = cl.text("--wire", "auto");
+    if (wire_s == "f16") p.wire = EFA_WIRE_F16;
+    else if (wire_s == "f32") p.wire = EFA_WIRE_F32;
+    else if (wire_s != "auto") fail("--wire must be auto, f16 or f32");
     if (const char* why = efa_attn_check_params(&p)) {
         if (g_rank == 0) fprintf(stderr, "ERROR: invalid params: %s\n", why);
         MPI_Abort(MPI_COMM_WORLD, 1);
@@ -197,7 +201,12 @@ int main(int argc, char** argv)
     efa_weights dw;
     void* output = nullptr;
     CUDA_OK(cudaMalloc(&dw.Qh, qkv_n * 2)); CUDA_OK(cudaMalloc(&dw.Kh, qkv_n * 2)); CUDA_OK(cudaMalloc(&dw.Vh, qkv_n * 2));
-    CUDA_OK(cudaMalloc(&dw.W_O, wo_n * 2)); CUDA_OK(cudaMalloc(&output, out_n * (proj_f32 ? 4 : 2)));
+    CUDA_OK(cudaMalloc(&dw.W_O, wo_n * 2));
+    // With the multicast reduction the output lives in the context's symmetric region, where the switch writes it in
+    // place; --own_output keeps the reference's arrangement (the caller's cudaMalloc, one extra device copy per reduction).
+    const bool symmetric_out = p.reduce == EFA_REDUCE_NVLS && world > 1 && !p.skip_comm && !cl.on("--own_output");
+    if (symmetric_out) EFA_OK(efa_nvls_output(ctx, &p, &output));
+    else CUDA_OK(cudaMalloc(&output, out_n * (proj_f32 ? 4 : 2)));
     CUDA_OK(cudaMemcpy(dw.Qh, hq.data(), qkv_n * 2, cudaMemcpyHostToDevice));
     CUDA_OK(cudaMemcpy(dw.Kh, hk.data(), qkv_n * 2, cudaMemcpyHostToDevice));
     CUDA_OK(cudaMemcpy(dw.Vh, hv.data(), qkv_n * 2, cudaMemcpyHostToDevice));
@@ -239,7 +248,8 @@ int main(int argc, char** argv)
             fflush(stdout);
         }
     }
-    cudaFree(dw.Qh); cudaFree(dw.Kh); cudaFree(dw.Vh); cudaFree(dw.W_O); cudaFree(output); cudaFree(residual);
+    cudaFree(dw.Qh); cudaFree(dw.Kh); cudaFree(dw.Vh); cudaFree(dw.W_O); cudaFree(residual);
+    if (!symmetric_out) cudaFree(output);
     EFA_OK(efa_destroy_ctx(ctx));
     MPI_Finalize();
     return 0;

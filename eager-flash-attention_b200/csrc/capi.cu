@@ -1,12 +1,16 @@
 // extern "C" surface of the library: argument checks, then the C++ implementation.
 #include "fa_fwd_sm100.cuh"
 #include "host_util.h"
+#include "nvls_reduce.h"
 #include "runtime.h"
 
 #include <cuda_fp16.h>
 
 #include <chrono>
 #include <cstring>
+
+#include <sys/mman.h>
+#include <unistd.h>
 
 using namespace efa;
 
@@ -28,6 +32,12 @@ extern "C" int efa_flash_attn_tc_forward_noalloc(const void* Q, const void* K, c
 {
     if (!Q || !K || !V || !p) { set_error("efa_flash_attn_tc_forward_noalloc: null argument"); return 2; }
     return fa_forward_noalloc(Q, K, V, O, o_dtype, q_start, q_rows, *p, (cudaStream_t)stream);
+}
+
+extern "C" int efa_flash_attn_tc_noalloc_status(int* out4, int reset)
+{
+    if (!out4) { set_error("efa_flash_attn_tc_noalloc_status: null argument"); return 2; }
+    return noalloc_status(out4, reset);
 }
 
 extern "C" int efa_flash_attn_tc_combine(const efa_flash_partials* part, void* O, int o_dtype,
@@ -177,5 +187,22 @@ extern "C" int efa_world_selftest(const efa_world* w)
     for (int r = 0; r < w->size; r++)
         for (int i = 0; i < 64; i++)
             if (all[r * 64 + i] != (unsigned char)(r * 3 + i)) { set_error("efa_world_selftest: all-gather slot %d wrong", r); return 1; }
+    // A file descriptor from rank 0 to the others (how the handle of a multicast object travels): an anonymous
+    // file with a known word in it; every receiver reads the word through its own descriptor.
+    int fd = -1, got = -1;
+    const unsigned magic = 0x0efab200u;
+    if (w->rank == 0) {
+        fd = memfd_create("efa-selftest", 0);
+        if (fd < 0 || write(fd, &magic, sizeof(magic)) != (ssize_t)sizeof(magic)) { set_error("efa_world_selftest: memfd"); if (fd >= 0) close(fd); fd = -1; }
+    }
+    int bad = share_fd(*w, fd, &got) != 0;
+    if (!bad && w->rank != 0) {
+        unsigned word = 0;
+        bad = pread(got, &word, sizeof(word), 0) != (ssize_t)sizeof(word) || word != magic;
+        close(got);
+    }
+    if (fd >= 0) close(fd);
+    double vote = bad ? 1.0 : 0.0;
+    if (w->allreduce_max_f64(w->user, &vote) || vote != 0.0) { set_error("efa_world_selftest: passing a file descriptor between the ranks failed"); return 1; }
     return 0;
 }

@@ -564,24 +564,32 @@ namespace efa {
 namespace {
 
 static __device__ __align__(256) float g_static_scratch[EFA_STATIC_SCRATCH_BYTES / sizeof(float)];
+// Status word of the kernels launched by this entry point ({code, block, site, 0}), in the module for the same
+// reason: the status word of the other entry points is allocated memory.
+static __device__ int g_noalloc_status[4];
 
 // In host code `g_static_scratch` is only a handle for the symbol, not a device address: the address
 // that kernels may use comes from cudaGetSymbolAddress, once per device, with that device current.
-int static_scratch_address(float** out)
+int static_scratch_address(float** out, int** status_out)
 {
     static float* addr[64] = {};
+    static int* status[64] = {};
     static std::mutex mu;
     int dev = 0;
     EFA_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) { set_error("device ordinal %d out of range", dev); return 1; }
     std::lock_guard<std::mutex> lock(mu);
-    if (!addr[dev]) {
+    if (!addr[dev] || !status[dev]) {
         void* p = nullptr;
+        void* q = nullptr;
         EFA_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
-        if (!p) { set_error("cudaGetSymbolAddress returned a null address for the static scratch"); return 1; }
+        EFA_CUDA(cudaGetSymbolAddress(&q, g_noalloc_status));
+        if (!p || !q) { set_error("cudaGetSymbolAddress returned a null address for the static scratch"); return 1; }
         addr[dev] = static_cast<float*>(p);
+        status[dev] = static_cast<int*>(q);
     }
     *out = addr[dev];
+    *status_out = status[dev];
     return 0;
 }
 
@@ -618,7 +626,8 @@ int fa_forward_noalloc(const void* Q, const void* K, const void* V, void* O, int
         return 6;
     }
     float* scratch = nullptr;
-    if (static_scratch_address(&scratch)) return 1;
+    int* status = nullptr;
+    if (static_scratch_address(&scratch, &status)) return 1;
 
     CUtensorMap tq, tk, tv;
     if (encode_qkv_tmap_uncached(Q, p.S, p.H_local, p.d_h, &tq) || encode_qkv_tmap_uncached(K, p.S, p.H_local, p.d_h, &tk) ||
@@ -636,7 +645,7 @@ int fa_forward_noalloc(const void* Q, const void* K, const void* V, void* O, int
     a.nsplit = p.split; a.kv_len = p.S / p.split; a.causal = p.causal;
     a.scale_log2e = p.scale * 1.4426950408889634f;
     a.tile_counters = nullptr; a.tile_rows = 0;
-    a.status = nullptr;                      // the status word of the other entry points is allocated memory
+    a.status = status;                       // a word of the module, see noalloc_status()
     a.band_blocks = 0;
     a.heavy_first = 0;
 
@@ -651,6 +660,18 @@ int fa_forward_noalloc(const void* Q, const void* K, const void* V, void* O, int
     }
     if (rc) return rc;
     return fa_combine(part, O, o_dtype, 0, q_rows, p, stream);
+}
+
+// Status of the kernels launched by fa_forward_noalloc on the current device (and optionally clears it).
+// Copies to and from a symbol of the module: no allocation here either.
+int noalloc_status(int* out4, int reset)
+{
+    EFA_CUDA(cudaMemcpyFromSymbol(out4, g_noalloc_status, 4 * sizeof(int)));
+    if (reset) {
+        const int zero[4] = {0, 0, 0, 0};
+        EFA_CUDA(cudaMemcpyToSymbol(g_noalloc_status, zero, sizeof(zero)));
+    }
+    return 0;
 }
 
 }  // namespace efa

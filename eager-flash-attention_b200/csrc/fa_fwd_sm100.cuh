@@ -22,6 +22,9 @@ int fa_forward(const void* Q, const void* K, const void* V, void* O, int o_dtype
 int fa_forward_noalloc(const void* Q, const void* K, const void* V, void* O, int o_dtype,
                        int q_start, int q_rows, const efa_flash_params& p, cudaStream_t stream);
 
+// {code, block, site, 0} written by a kernel of fa_forward_noalloc whose bounded wait ran out; reset != 0 clears it.
+int noalloc_status(int* out4, int reset);
+
 int fa_combine(const efa_flash_partials& part, void* O, int o_dtype, int row0, int rows,
                const efa_flash_params& p, cudaStream_t stream);
 

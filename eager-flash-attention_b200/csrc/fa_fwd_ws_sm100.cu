@@ -5,13 +5,26 @@
 // One CTA = 256 query rows (two 128-row Q tiles) of one (head, split), 384 threads:
 //   warps 0-3   softmax of Q tile 0        (one thread per row; registers raised with setmaxnreg)
 //   warps 4-7   softmax of Q tile 1
-//   warp  8     TMA producer: Q tiles once, then K and V 128-key stages through a ring
+//   warp  8     TMA producer: Q tiles once, then K and V 128-key stages through two rings
 //   warp  9     tcgen05.mma issuer; owns the tensor-memory allocation
 //   warps 10-11 idle (they give their registers to the softmax warps)
-// Both Q tiles share each K/V stage, which halves the L2 -> shared-memory traffic per FLOP. The MMA
-// warp interleaves the tiles so that while one tile's softmax runs on the SIMT pipes the tensor
-// pipe executes the other tile's P*V and the next Q*K^T:
+// Both Q tiles share each K/V stage, which halves the L2 -> shared-memory traffic per FLOP. Each tile is a
+// chain  S(j) -> softmax -> P(j) -> P(j)*V(j) -> Q*K^T(j+1) -> S(j+1)  (P overwrites S in tensor memory, and the
+// tensor pipe executes in issue order), and the two chains run half a period apart: the one issuing thread
+// serves them in turn,
 //     ... PV0(j) QK0(j+1) | PV1(j) QK1(j+1) | PV0(j+1) QK0(j+2) | ...
+// so that while one tile's softmax runs on the SIMT pipes (and has the special-function unit to itself) the
+// tensor pipe executes the other tile's MMAs. A period is one softmax plus one tile's MMAs; timestamps taken
+// inside the kernel (d_h = 128) put it at about 1770 + 1890 cycles against 2048 cycles of pure MMA time for
+// both tiles. Two things were tried against that and measured slower: an issuing thread per tile (the tiles fall
+// into step, both softmaxes then share the special-function unit and both MMA groups the tensor pipe), and
+// 64-key stages with two S buffers per tile so that Q*K^T runs a stage ahead (a 128x64x16 MMA takes 48 cycles,
+// not 32, and the issuing thread needs about as long per MMA as the tensor pipe). What did pay: descriptors kept
+// in registers as (low, high) words, so that an MMA costs the issuing thread two additions and the instruction
+// (it shares its scheduler with two softmax warps); a V ring one slot deeper than the K ring (V(j) is wanted
+// right at the start of stage j, K(j+1) a whole stage after its slot is freed); packed fp32 pairs in the softmax.
+// Computing a share of the exponentials with a polynomial on the FMA pipes lengthens the softmax and with it the
+// chain; it was measured slower at every share.
 // Tensor memory (512 columns): S0/P0 [0,128) S1/P1 [128,256) O0 [256,256+D) O1 [384,384+D).
 // O is rescaled in tensor memory by the softmax warps themselves, and only when a row maximum grew
 // by more than 2^8 since the value last used as the exponent offset (P then stays below 256, well
@@ -33,13 +46,6 @@
 
 #include <cmath>
 
-// Compile-time experiment switch: scale-and-offset and the row sum on packed pairs (fma.rn.f32x2 / add.rn.f32x2,
-// two fp32 lanes per instruction, same rounding as the scalar forms), which takes a quarter of the instructions
-// out of the softmax loop. Not yet measured; off.
-#ifndef EFA_F32X2
-#define EFA_F32X2 0
-#endif
-
 namespace efa {
 
 namespace {
@@ -57,8 +63,9 @@ struct WsCfg {
     static constexpr int NBOX       = D / 64;
     static constexpr int BOX_BYTES  = 128 * SWB;                 // 16 KB
     static constexpr int TILE_BYTES = 128 * D * 2;
-    static constexpr int NSTAGE     = D == 128 ? 2 : 4;
-    static constexpr int SMEM_BYTES = TILE_BYTES * (2 + 2 * NSTAGE) + 1024;
+    static constexpr int NSTAGE_K   = D == 128 ? 2 : 4;           // K(j+1) is wanted a whole stage after its slot is freed,
+    static constexpr int NSTAGE_V   = D == 128 ? 3 : 4;           // V(j) right at the start of the stage: the deeper ring
+    static constexpr int SMEM_BYTES = TILE_BYTES * (2 + NSTAGE_K + NSTAGE_V) + 1024;
     static constexpr int TMEM_COLS  = 512;
 };
 
@@ -69,7 +76,8 @@ __device__ __forceinline__ float max3(float a, float b, float c)
     return r;
 }
 
-#if EFA_F32X2
+// Two fp32 lanes per instruction (fma.rn.f32x2 / add.rn.f32x2: same rounding as the scalar forms): scale-and-offset
+// and the row sum of the softmax take half the instructions. Measured: 3 % of the attention launch.
 __device__ __forceinline__ uint64_t pack2(float lo, float hi)
 {
     uint64_t r;
@@ -92,7 +100,10 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b)
     asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
     return d;
 }
-#endif
+
+
+
+
 
 __device__ __forceinline__ void setmaxnreg_dec_56() { asm volatile("setmaxnreg.dec.sync.aligned.u32 56;"); }
 __device__ __forceinline__ void setmaxnreg_inc_224() { asm volatile("setmaxnreg.inc.sync.aligned.u32 224;"); }
@@ -112,16 +123,16 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ,
     constexpr uint32_t SWZ = swizzle_code(128);
     constexpr uint32_t IDESC_QK = idesc_f16_f32(WS_BM, WS_BN, 0, 0);
     constexpr uint32_t IDESC_PV = idesc_f16_f32(WS_BM, D, 0, 1);
-    constexpr int NST = C::NSTAGE;
+    constexpr int NSK = C::NSTAGE_K, NSV = C::NSTAGE_V;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* sQ = smem;                                   // 2 tiles
-    uint8_t* sK = sQ + 2 * C::TILE_BYTES;                 // NST stages
-    uint8_t* sV = sK + NST * C::TILE_BYTES;               // NST stages
+    uint8_t* sK = sQ + 2 * C::TILE_BYTES;                 // NSK stages
+    uint8_t* sV = sK + NSK * C::TILE_BYTES;               // NSV stages
 
     __shared__ __align__(8) uint64_t q_full[2];
-    __shared__ __align__(8) uint64_t k_full[NST], k_empty[NST], v_full[NST], v_empty[NST];
+    __shared__ __align__(8) uint64_t k_full[NSK], k_empty[NSK], v_full[NSV], v_empty[NSV];
     __shared__ __align__(8) uint64_t s_full[2], p_full[2][2], o_done[2];
     __shared__ uint32_t tmem_base_smem;
     __shared__ int abort_word;
@@ -156,7 +167,8 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ,
             half_done[0][0] = half_done[0][1] = half_done[1][0] = half_done[1][1] = 0;
             if (round > 0) {
                 for (int q = 0; q < 2; q++) { mbar_inval(&q_full[q]); mbar_inval(&s_full[q]); mbar_inval(&p_full[q][0]); mbar_inval(&p_full[q][1]); mbar_inval(&o_done[q]); }
-                for (int s = 0; s < NST; s++) { mbar_inval(&k_full[s]); mbar_inval(&k_empty[s]); mbar_inval(&v_full[s]); mbar_inval(&v_empty[s]); }
+                for (int s = 0; s < NSK; s++) { mbar_inval(&k_full[s]); mbar_inval(&k_empty[s]); }
+                for (int s = 0; s < NSV; s++) { mbar_inval(&v_full[s]); mbar_inval(&v_empty[s]); }
             }
             for (int q = 0; q < 2; q++) {
                 mbar_init(&q_full[q], 1);
@@ -165,10 +177,8 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ,
                 mbar_init(&p_full[q][1], WS_BM);
                 mbar_init(&o_done[q], 1);
             }
-            for (int s = 0; s < NST; s++) {
-                mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
-                mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
-            }
+            for (int s = 0; s < NSK; s++) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
+            for (int s = 0; s < NSV; s++) { mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
             mbar_fence_init();
         }
         __syncthreads();
@@ -242,30 +252,37 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ,
                 for (int q = 0; q < 2; q++)
                     if (nblk[q] > 0) load_tile(sQ + q * C::TILE_BYTES, &tmQ, &q_full[q], q_abs0[q]);
                 for (int j = 0; j < nblk_max; j++) {
-                    const int s = j % NST, u = j / NST;
-                    if (u > 0 && !mbar_wait(&k_empty[s], (uint32_t)((u - 1) & 1), &abort_word, 21)) break;
-                    load_tile(sK + s * C::TILE_BYTES, &tmK, &k_full[s], kv_lo + j * WS_BN);
-                    if (u > 0 && !mbar_wait(&v_empty[s], (uint32_t)((u - 1) & 1), &abort_word, 22)) break;
-                    load_tile(sV + s * C::TILE_BYTES, &tmV, &v_full[s], kv_lo + j * WS_BN);
+                    const int sk = j % NSK, uk = j / NSK, sv = j % NSV, uv = j / NSV;
+                    if (uk > 0 && !mbar_wait(&k_empty[sk], (uint32_t)((uk - 1) & 1), &abort_word, 21)) break;
+                    load_tile(sK + sk * C::TILE_BYTES, &tmK, &k_full[sk], kv_lo + j * WS_BN);
+                    if (uv > 0 && !mbar_wait(&v_empty[sv], (uint32_t)((uv - 1) & 1), &abort_word, 22)) break;
+                    load_tile(sV + sv * C::TILE_BYTES, &tmV, &v_full[sv], kv_lo + j * WS_BN);
                 }
             } else if (warp == 9 && lane == 0) {
-                // ---- MMA issuer
-                auto issue_qk = [&](int q, int stage) {
-                    const uint32_t qa = smem_u32(sQ + q * C::TILE_BYTES);
-                    const uint32_t ka = smem_u32(sK + stage * C::TILE_BYTES);
+                // ---- MMA issuer. Descriptors as (low, high) words; a k-step or a ring slot only moves the address
+                // field of the low word.
+                const uint64_t dq0 = smem_desc(smem_u32(sQ), 16, 1024, SWZ);
+                const uint64_t dk0 = smem_desc(smem_u32(sK), 16, 1024, SWZ);
+                const uint64_t dv0 = smem_desc(smem_u32(sV), C::BOX_BYTES, 1024, SWZ);
+                const uint32_t dq_lo = (uint32_t)dq0, dq_hi = (uint32_t)(dq0 >> 32);
+                const uint32_t dk_lo = (uint32_t)dk0, dk_hi = (uint32_t)(dk0 >> 32);
+                const uint32_t dv_lo = (uint32_t)dv0, dv_hi = (uint32_t)(dv0 >> 32);
+                auto issue_qk = [&](int q, int slot) {
+                    const uint32_t qa = dq_lo + (uint32_t)q * (C::TILE_BYTES >> 4);
+                    const uint32_t ka = dk_lo + (uint32_t)slot * (C::TILE_BYTES >> 4);
+                    const uint32_t tS = tmem_base + q * 128;
                     #pragma unroll
                     for (int ks = 0; ks < D / 16; ks++) {
-                        const uint32_t off = (uint32_t)((ks * 16) / C::BOXC) * C::BOX_BYTES + (uint32_t)((ks * 16) % C::BOXC) * 2u;
-                        tc_mma_ss(tmem_base + q * 128, smem_desc(qa + off, 16, 1024, SWZ), smem_desc(ka + off, 16, 1024, SWZ),
-                                  IDESC_QK, ks > 0 ? 1u : 0u);
+                        const uint32_t off = ((uint32_t)((ks * 16) / C::BOXC) * C::BOX_BYTES + (uint32_t)((ks * 16) % C::BOXC) * 2u) >> 4;
+                        tc_mma_ss_lh(tS, qa + off, dq_hi, ka + off, dk_hi, IDESC_QK, ks > 0 ? 1u : 0u);
                     }
                 };
-                auto issue_pv = [&](int q, int stage, bool first, int half) {
-                    const uint32_t va = smem_u32(sV + stage * C::TILE_BYTES);
+                auto issue_pv = [&](int q, int slot, uint32_t acc0, int half) {
+                    const uint32_t va = dv_lo + (uint32_t)slot * (C::TILE_BYTES >> 4);
+                    const uint32_t tS = tmem_base + q * 128, tO = tmem_base + 256 + q * 128;
                     #pragma unroll
                     for (int ks = half * 4; ks < half * 4 + 4; ks++)
-                        tc_mma_ts(tmem_base + 256 + q * 128, tmem_base + q * 128 + ks * 8,
-                                  smem_desc(va + ks * 16 * 128, C::BOX_BYTES, 1024, SWZ), IDESC_PV, (!first || ks > 0) ? 1u : 0u);
+                        tc_mma_ts_lh(tO, tS + ks * 8, va + ((ks * 16 * 128) >> 4), dv_hi, IDESC_PV, ks > 0 ? 1u : acc0);
                 };
                 bool ok = true;
                 if (nblk_max > 0) {
@@ -282,8 +299,8 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ,
                     if (ok) tc_commit(&k_empty[0]);
                 }
                 for (int j = 0; j < nblk_max && ok; j++) {
-                    const int s = j % NST;
-                    ok = mbar_wait(&v_full[s], (uint32_t)((j / NST) & 1), &abort_word, 25);
+                    const int sv = j % NSV;
+                    ok = mbar_wait(&v_full[sv], (uint32_t)((j / NSV) & 1), &abort_word, 25);
                     if (!ok) break;
                     bool k_next_ready = false;
                     for (int q = 0; q < 2 && ok; q++) {
@@ -291,32 +308,32 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ,
                         ok = mbar_wait(&p_full[q][0], (uint32_t)(j & 1), &abort_word, 26);
                         if (!ok) break;
                         tc_fence_after_sync();
-                        issue_pv(q, s, j == 0, 0);
+                        issue_pv(q, sv, j > 0 ? 1u : 0u, 0);
                         ok = mbar_wait(&p_full[q][1], (uint32_t)(j & 1), &abort_word, 29);
                         if (!ok) break;
                         tc_fence_after_sync();
-                        issue_pv(q, s, j == 0, 1);
+                        issue_pv(q, sv, 1u, 1);
                         if (j + 1 < nblk[q]) {
-                            const int ns = (j + 1) % NST;
+                            const int sk = (j + 1) % NSK;
                             if (!k_next_ready) {
-                                ok = mbar_wait(&k_full[ns], (uint32_t)(((j + 1) / NST) & 1), &abort_word, 27);
+                                ok = mbar_wait(&k_full[sk], (uint32_t)(((j + 1) / NSK) & 1), &abort_word, 27);
                                 if (!ok) break;
                                 tc_fence_after_sync();
                                 k_next_ready = true;
                             }
-                            issue_qk(q, ns);
+                            issue_qk(q, sk);
                             tc_commit(&s_full[q]);
                         } else {
                             tc_commit(&o_done[q]);
                         }
                     }
                     if (!ok) break;
-                    tc_commit(&v_empty[s]);
-                    if (j + 1 < nblk_max) tc_commit(&k_empty[(j + 1) % NST]);
+                    tc_commit(&v_empty[sv]);
+                    if (j + 1 < nblk_max) tc_commit(&k_empty[(j + 1) % NSK]);
                 }
                 // The last commit has to land before the barriers are rebuilt for the next work item.
                 if (ok && nblk_max > 0)
-                    mbar_wait(&v_empty[(nblk_max - 1) % NST], (uint32_t)(((nblk_max - 1) / NST) & 1), &abort_word, 28);
+                    mbar_wait(&v_empty[(nblk_max - 1) % NSV], (uint32_t)(((nblk_max - 1) / NSV) & 1), &abort_word, 28);
             }
             end_item();
             if (!PERSIST) break;
@@ -404,31 +421,18 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ,
 
                 // P is handed to the MMA warp in two halves of 64 keys: the first four k-steps of P*V run on
                 // the tensor pipe while the exponentials of the second half are still being computed.
-                float ps0 = 0.f, ps1 = 0.f;
-#if EFA_F32X2
                 const uint64_t scale2 = pack2(a.scale_log2e, a.scale_log2e), off2 = pack2(-m_off, -m_off);
                 uint64_t psum2[2] = {pack2(0.f, 0.f), pack2(0.f, 0.f)};
-#endif
                 #pragma unroll
                 for (int c = 0; c < 4; c++) {
                     uint32_t pk[16];
                     #pragma unroll
                     for (int i = 0; i < 16; i++) {
-#if EFA_F32X2
                         float x0, x1;
                         unpack2(fma2(pack2(__uint_as_float(su[c][2 * i]), __uint_as_float(su[c][2 * i + 1])), scale2, off2), x0, x1);
                         const float q0 = ex2(x0), q1 = ex2(x1);
                         psum2[i & 1] = add2(psum2[i & 1], pack2(q0, q1));
                         pk[i] = pack_f16x2(q0, q1);
-#else
-                        const float x0 = fmaf(__uint_as_float(su[c][2 * i]),     a.scale_log2e, -m_off);
-                        const float x1 = fmaf(__uint_as_float(su[c][2 * i + 1]), a.scale_log2e, -m_off);
-                        const float p0 = ex2(x0);
-                        const float p1 = ex2(x1);
-                        ps0 += p0;
-                        ps1 += p1;
-                        pk[i] = pack_f16x2(p0, p1);
-#endif
                     }
                     tmem_st16(tmem_S + c * 16, pk);
                     if (c == 1 || c == 3) {
@@ -437,7 +441,7 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ,
                         mbar_arrive(&p_full[q][c >> 1]);
                     }
                 }
-#if EFA_F32X2
+                float ps0, ps1;
                 {
                     float s0, s1, s2, s3;
                     unpack2(psum2[0], s0, s1);
@@ -445,7 +449,6 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ,
                     ps0 = s0 + s2;
                     ps1 = s1 + s3;
                 }
-#endif
                 l_run = l_run * alpha + (ps0 + ps1);
             }
 

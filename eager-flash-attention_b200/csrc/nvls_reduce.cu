@@ -33,7 +33,7 @@
 struct NvlsState {
     int R = 0, rank = 0;
     size_t size = 0;                 // bytes mapped (flags + partial sums + results)
-    size_t data_bytes = 0;           // capacity of each of the two data regions
+    size_t data_bytes = 0;           // capacity of the result region (fp16); the partial sums have twice that (room for fp32)
     CUmemGenericAllocationHandle mem = 0, mc = 0;
     CUdeviceptr uc = 0, mcva = 0;    // this rank's memory; the multicast view of all ranks' memory
     CUdevice dev = 0;
@@ -54,7 +54,7 @@ struct NvArgs {
     char*       mc_out;        // multicast view of the result buffers
     unsigned*   flags_mc;      // multicast view of this slot's flags
     const unsigned* flags_uc;  // this rank's copy of them
-    size_t      first16, n16;  // range in 16-byte units
+    size_t      first16, n16;  // range in units of 8 elements (16 bytes of fp16)
     int         R, rank;
     unsigned    target_start, target_end;
     unsigned long long limit_ns;
@@ -75,6 +75,13 @@ __device__ __forceinline__ uint4 multimem_ld_reduce_f16(const char* mc_addr)
 {
     uint4 v;
     asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc_addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint4 multimem_ld_reduce_f32(const char* mc_addr)
+{
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc_addr) : "memory");
     return v;
 }
@@ -99,9 +106,13 @@ __device__ __forceinline__ bool block_barrier(const NvArgs& a, unsigned target, 
     }
 }
 
+// WIRE_F32: the partial sums are fp32 (two 16-byte loads per 8 elements, summed in fp32 by the switch, rounded here,
+// once); otherwise fp16 (one load per 8 elements, fp32 accumulation and the rounding inside the switch).
+template <bool WIRE_F32>
 __global__ void __launch_bounds__(NV_THREADS)
 nvls_allreduce_kernel(const NvArgs a)
 {
+    constexpr int UNROLL = WIRE_F32 ? 4 : 8;              // 16-byte loads in flight per thread: 8
     __shared__ int abort_word;
     if (threadIdx.x == 0) {
         abort_word = 0;
@@ -113,13 +124,26 @@ nvls_allreduce_kernel(const NvArgs a)
         const size_t per = (a.n16 + a.R - 1) / a.R;
         const size_t lo = min((size_t)a.rank * per, a.n16), hi = min(lo + per, a.n16);
         const size_t stride = (size_t)gridDim.x * NV_THREADS;
-        for (size_t i = lo + (size_t)blockIdx.x * NV_THREADS + threadIdx.x; i < hi; i += 4 * stride) {
-            uint4 v[4];
+        for (size_t i = lo + (size_t)blockIdx.x * NV_THREADS + threadIdx.x; i < hi; i += UNROLL * stride) {
+            uint4 v[UNROLL];
             #pragma unroll
-            for (int u = 0; u < 4; u++)
-                if (i + u * stride < hi) v[u] = multimem_ld_reduce_f16(a.mc_send + (a.first16 + i + u * stride) * 16);
+            for (int u = 0; u < UNROLL; u++) {
+                const size_t e = a.first16 + i + u * stride;
+                if (i + u * stride < hi) {
+                    if (WIRE_F32) {
+                        const uint4 x = multimem_ld_reduce_f32(a.mc_send + e * 32);
+                        const uint4 y = multimem_ld_reduce_f32(a.mc_send + e * 32 + 16);
+                        v[u].x = pack_f16x2(__uint_as_float(x.x), __uint_as_float(x.y));
+                        v[u].y = pack_f16x2(__uint_as_float(x.z), __uint_as_float(x.w));
+                        v[u].z = pack_f16x2(__uint_as_float(y.x), __uint_as_float(y.y));
+                        v[u].w = pack_f16x2(__uint_as_float(y.z), __uint_as_float(y.w));
+                    } else {
+                        v[u] = multimem_ld_reduce_f16(a.mc_send + e * 16);
+                    }
+                }
+            }
             #pragma unroll
-            for (int u = 0; u < 4; u++)
+            for (int u = 0; u < UNROLL; u++)
                 if (i + u * stride < hi) multimem_st(a.mc_out + (a.first16 + i + u * stride) * 16, v[u]);
         }
     }
@@ -181,6 +205,8 @@ socklen_t abstract_addr(sockaddr_un* addr, const char* name)
     return (socklen_t)(offsetof(sockaddr_un, sun_path) + 1 + len);
 }
 
+}  // namespace
+
 // Rank 0 passes `fd_root`; every other rank receives its own descriptor for the same object in *fd_out.
 // Returns 0 on this rank's success (the caller votes over the ranks afterwards).
 int share_fd(const efa_world& w, int fd_root, int* fd_out)
@@ -225,6 +251,8 @@ int share_fd(const efa_world& w, int fd_root, int* fd_out)
     return rc;
 }
 
+namespace {
+
 // Every rank learns whether all ranks succeeded (a failure on one rank must not leave the others inside
 // the next collective step).
 bool all_ok(const efa_world& w, bool mine)
@@ -264,7 +292,7 @@ int create_region(efa_ctx* c, NvlsState* st, size_t data_bytes)
     std::memset(&mp, 0, sizeof(mp));
     mp.numDevices = (unsigned)R;
     mp.handleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
-    mp.size = NV_FLAG_BYTES + 2 * data_bytes;
+    mp.size = NV_FLAG_BYTES + 3 * data_bytes;                     // flags, partial sums (fp32 capable), fp16 results
     CUmemAllocationProp ap;
     std::memset(&ap, 0, sizeof(ap));
     ap.type = CU_MEM_ALLOCATION_TYPE_PINNED;
@@ -357,13 +385,15 @@ int nvls_prepare(efa_ctx* c, const efa_params& p)
     release_local(st);
     if (world_barrier(c->world)) return 1;
     const size_t data = (want + 4095) / 4096 * 4096;
+    // The grid of the reduction kernel is fixed for the life of a region (flag b counts the barriers of block b).
+    c->nvls_ctas = (p.reduce_ctas >= 1 && p.reduce_ctas <= NV_MAX_CTAS) ? p.reduce_ctas : 16;
     return create_region(c, st, data);
 }
 
 void* nvls_send_buf(efa_ctx* c) { return c->nvls && c->nvls->size ? (void*)(c->nvls->uc + NV_FLAG_BYTES) : nullptr; }
-void* nvls_result_buf(efa_ctx* c) { return c->nvls && c->nvls->size ? (void*)(c->nvls->uc + NV_FLAG_BYTES + c->nvls->data_bytes) : nullptr; }
+void* nvls_result_buf(efa_ctx* c) { return c->nvls && c->nvls->size ? (void*)(c->nvls->uc + NV_FLAG_BYTES + 2 * c->nvls->data_bytes) : nullptr; }
 
-int nvls_allreduce(efa_ctx* c, int slot, size_t first, size_t n, cudaStream_t stream)
+int nvls_allreduce(efa_ctx* c, int slot, size_t first, size_t n, bool wire_f32, cudaStream_t stream)
 {
     NvlsState* st = c->nvls;
     if (!st || !st->size) { set_error("nvls_allreduce without nvls_prepare"); return 2; }
@@ -375,7 +405,7 @@ int nvls_allreduce(efa_ctx* c, int slot, size_t first, size_t n, cudaStream_t st
     if (n == 0) return 0;
     NvArgs a;
     a.mc_send = (const char*)(st->mcva + NV_FLAG_BYTES);
-    a.mc_out = (char*)(st->mcva + NV_FLAG_BYTES + st->data_bytes);
+    a.mc_out = (char*)(st->mcva + NV_FLAG_BYTES + 2 * st->data_bytes);
     a.flags_mc = (unsigned*)st->mcva + (size_t)slot * NV_MAX_CTAS;
     a.flags_uc = (const unsigned*)st->uc + (size_t)slot * NV_MAX_CTAS;
     a.first16 = first / 8; a.n16 = n / 8;
@@ -386,7 +416,8 @@ int nvls_allreduce(efa_ctx* c, int slot, size_t first, size_t n, cudaStream_t st
     a.limit_ns = c->wait_limit_ns;
     a.status = kernel_status_word();
     // The grid is the same for every call of the context: flag b counts the barriers of block b.
-    nvls_allreduce_kernel<<<c->nvls_ctas, NV_THREADS, 0, stream>>>(a);
+    if (wire_f32) nvls_allreduce_kernel<true><<<c->nvls_ctas, NV_THREADS, 0, stream>>>(a);
+    else          nvls_allreduce_kernel<false><<<c->nvls_ctas, NV_THREADS, 0, stream>>>(a);
     EFA_CUDA(cudaGetLastError());
     return 0;
 }

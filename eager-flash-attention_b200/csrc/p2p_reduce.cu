@@ -565,7 +565,7 @@ int p2p_launch(efa_ctx* c, const efa_params& p, const efa_weights& w, const void
     a.tile = p.tile;
     a.GS = (p.R > 1) ? a.NBR : 1;
     // Counters and flags only grow; the targets wrap with them (see wait_flag).
-    a.tile_target = (int)(unsigned)((unsigned long long)st->epoch * (unsigned long long)st->target);
+    a.tile_target = (int)(unsigned)((unsigned long long)st->epoch * (unsigned long long)st->target) + p.debug_target_bias;
     a.arrive_target = (int)(unsigned)((unsigned long long)st->epoch * (unsigned long long)(p.R * (a.NBR / a.GS)));
     a.done_target = a.arrive_target;
     a.flag_wait_ns = c->wait_limit_ns;

@@ -220,7 +220,7 @@ extern "C" int efa_make_params(efa_params* out, int S, int d, int H, int tile, i
     p.group_tiles = 0;
     p.proj_f32 = 0;
     p.row_order = EFA_ROWS_AUTO;
-    p.reduce_ctas = 0; p.band_rows = 0; p.reserve_sms = 0; p.trace = 0;
+    p.reduce_ctas = 0; p.band_rows = 0; p.reserve_sms = 0; p.trace = 0; p.wire = EFA_WIRE_AUTO; p.debug_target_bias = 0;
     const float scale = p.d_h > 0 ? 1.0f / sqrtf((float)p.d_h) : 0.f;
     p.flash_tc = efa_flash_params{S, p.d_h, p.H_local, split, causal, scale};
     *out = p;
@@ -339,7 +339,15 @@ extern "C" int efa_make_ctx(efa_ctx** out, const efa_world* world, int ncomm, in
     return 0;
 }
 
-namespace efa { void p2p_destroy(efa_ctx* c); void nvls_destroy(efa_ctx* c); }
+namespace efa { void p2p_destroy(efa_ctx* c); void nvls_destroy(efa_ctx* c); int nvls_prepare(efa_ctx* c, const efa_params& p); void* nvls_result_buf(efa_ctx* c); }
+
+extern "C" int efa_nvls_output(efa_ctx* c, const efa_params* p, void** output)
+{
+    if (!c || !p || !output) { set_error("efa_nvls_output: null argument"); return 2; }
+    if (nvls_prepare(c, *p)) return 1;
+    *output = nvls_result_buf(c);
+    return 0;
+}
 
 extern "C" int efa_ctx_set_wait_limit_ms(efa_ctx* c, double device_ms, double host_ms)
 {

@@ -71,12 +71,16 @@ struct Run {
     // `output` is fp16, or fp32 with proj_f32 (the reference's types).
     size_t esz() const { return p.proj_f32 ? sizeof(float) : sizeof(__half); }
     size_t row_bytes() const { return (size_t)p.d * esz(); }
-    // The partial sums that are reduced. NCCL adds fp16 values in fp16, one rounding per hop, which with more
-    // than two ranks exceeds what one final rounding costs (3.5e-3 against 1.7e-3 at outputs of magnitude 3.4
-    // with eight ranks). So with more than two ranks the NCCL path reduces the fp32 accumulators and rounds the
-    // sum once (the reference reduces fp32 too, run_drivers.cu:26-30); with two ranks one fp16 addition is one rounding
-    // either way. The multicast path accumulates in fp32 inside the switch and keeps fp16 on the wire.
-    bool wire_f32() const { return p.proj_f32 || (p.reduce == EFA_REDUCE_NCCL && p.R > 2 && !p.skip_comm); }
+    // The partial sums that cross the links (efa_params.wire): the fp32 accumulators by default, summed in fp32 and
+    // rounded once into the fp16 output, as the reference's types are (run_drivers.cu:26-30); fp16 on request (half
+    // the bytes; every partial sum then carries its own rounding, and NCCL rounds once more per hop). The fused
+    // peer-memory kernel stages fp16 and accumulates in fp32.
+    bool wire_f32() const
+    {
+        if (p.proj_f32) return true;
+        if (p.skip_comm || p.R == 1 || p.reduce == EFA_REDUCE_P2P) return false;
+        return p.wire != EFA_WIRE_F16;
+    }
     bool nvls() const { return p.reduce == EFA_REDUCE_NVLS && !p.skip_comm && p.R > 1; }
     size_t send_row_bytes() const { return (size_t)p.d * (wire_f32() ? sizeof(float) : sizeof(__half)); }
     char* send_base() const { return static_cast<char*>(nvls() ? nvls_send_buf(c) : c->send_buf); }
@@ -131,11 +135,13 @@ struct Run {
         cudaStream_t cs = c->comm_streams[slot];
         if (nvls()) {
             // the switch sums the ranks' send buffers into every rank's result buffer; one local copy to `output`
-            const size_t first = (size_t)(static_cast<char*>(send) - send_base()) / sizeof(__half);
+            const bool f32 = wire_f32();
+            const size_t first = (size_t)(static_cast<char*>(send) - send_base()) / (f32 ? sizeof(float) : sizeof(__half));
             launches++;
-            if (nvls_allreduce(c, slot, first, n, cs)) return 1;
-            EFA_CUDA(cudaMemcpyAsync(recv, static_cast<char*>(nvls_result_buf(c)) + first * sizeof(__half), n * sizeof(__half),
-                                     cudaMemcpyDeviceToDevice, cs));
+            if (nvls_allreduce(c, slot, first, n, f32, cs)) return 1;
+            char* landed = static_cast<char*>(nvls_result_buf(c)) + first * sizeof(__half);
+            if (landed != static_cast<char*>(recv))      // an output inside the region (efa_nvls_output) is written in place
+                EFA_CUDA(cudaMemcpyAsync(recv, landed, n * sizeof(__half), cudaMemcpyDeviceToDevice, cs));
         } else {
             const NcclApi* nccl = nccl_api();
             if (!nccl) return 1;
@@ -183,6 +189,7 @@ int sync_stream(efa_ctx* c, cudaStream_t s, int* counters, size_t ncounters)
             cudaStreamSynchronize(rescue);
             cudaStreamDestroy(rescue);
         }
+        cudaStreamSynchronize(s);            // nothing on it waits for a counter any more
     }
     set_error("stream did not finish within %.1f s; pending tile waits were released", deadline_ms / 1e3);
     return 4;
@@ -359,7 +366,7 @@ int run_stream(Run& r, char* output, efa_run_stats* st)
     __half* O_all = static_cast<__half*>(c->O_all);
     char* send_buf = r.send_base();
     int* counters = c->counters;
-    const int target = efa_blocks_per_tile(&p);
+    const int target = efa_blocks_per_tile(&p) + p.debug_target_bias;
     cudaEvent_t reset_done = c->events[p.num_tiles];
     const bool fused = (p.reduce == EFA_REDUCE_P2P) && !p.skip_comm && !p.skip_proj;
     // Launch plan (efa_stream_plan): groups of consecutive tiles per projection + reduction launch in the order in
@@ -447,9 +454,13 @@ int run_stream(Run& r, char* output, efa_run_stats* st)
         if (trace) cudaEventRecord(c->trace_events[3 * gidx + 2], c->comm_streams[slot]);
     }
     const double t_enqueued = now_ms() - t0;
-    if (sync_stream(c, c->compute_stream, counters, p.num_tiles)) return 1;
-    if (sync_stream(c, c->proj_stream, counters, p.num_tiles)) return 1;
-    if (sync_comm_streams(c)) return 1;
+    if (sync_stream(c, c->compute_stream, counters, p.num_tiles) || sync_stream(c, c->proj_stream, counters, p.num_tiles) ||
+        sync_comm_streams(c)) {
+        // a wait ran out and the counters were overwritten: let everything that was enqueued drain, then report
+        cudaStreamSynchronize(c->proj_stream);
+        for (int i = 0; i < c->ncomm; i++) cudaStreamSynchronize(c->comm_streams[i]);
+        return 1;
+    }
     const int rc = finish_timing(c, t0, st, true, false, r.launches);
     if (trace && rc == 0) {
         float attn_end = 0.f;

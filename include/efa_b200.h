@@ -90,10 +90,18 @@ int efa_flash_attn_tc_combine(const efa_flash_partials* part, void* O, int o_dty
  * the previous call's contents (nothing in it needs clearing: each call writes every element it
  * later reads). Two calls that overlap on the GPU (different streams, or different host threads) race on it:
  * order them on one stream or with events. Kernels launched here do not report to
- * efa_kernel_status. */
+ * efa_kernel_status (its word is allocated memory) but to a word of their own inside the library, read with
+ * efa_flash_attn_tc_noalloc_status. */
 int efa_flash_attn_tc_forward_noalloc(const void* Q, const void* K, const void* V,
                                       void* O, int o_dtype, int q_start, int q_rows,
                                       const efa_flash_params* p, void* stream);
+
+/* out4 = {code, block, site, 0} of the current device: code 0 = no kernel launched by
+ * efa_flash_attn_tc_forward_noalloc gave up a bounded wait since the word was last cleared; reset != 0 clears
+ * it after reading. A call whose kernel gave up leaves its output incomplete, so check after synchronising.
+ * Synchronous copies from and to a symbol of the library; allocates nothing. Like the entry point it belongs
+ * to, it has no counterpart in the reference. */
+int efa_flash_attn_tc_noalloc_status(int* out4, int reset);
 
 /* flash_attn_tc_check_params (flash_attn_tc.cuh:59-60, flash_attn_tc.cu:401-409):
  * NULL when the launch is legal, else a static description. */
@@ -142,6 +150,8 @@ int         efa_parse_mode(const char* s); /* parse_mode (run_drivers.cuh:20), -
  *         with multicast support; otherwise the call fails with a message (nothing falls back silently). */
 enum { EFA_REDUCE_NCCL = 0, EFA_REDUCE_P2P = 1, EFA_REDUCE_NVLS = 2 };
 
+enum { EFA_WIRE_AUTO = 0, EFA_WIRE_F16 = 1, EFA_WIRE_F32 = 2 };
+
 /* Order in which stream mode takes the rows of a causal problem (row_order). */
 enum { EFA_ROWS_AUTO = 0, EFA_ROWS_ASCENDING = 1, EFA_ROWS_DESCENDING = 2 };
 
@@ -173,6 +183,16 @@ typedef struct efa_params {
     int reserve_sms;            /* stream mode, diagnostics: > 0 runs the attention kernel in its persistent form and
                                    leaves that many SMs without an attention CTA */
     int trace;                  /* stream mode, diagnostics: 1 prints the timeline of the groups on stderr */
+    int wire;                   /* element type of the partial sums that cross the links (NCCL and NVLS reductions):
+                                   EFA_WIRE_F16 = the projection rounds its accumulator to fp16 and the reduction sums those
+                                   (fp32 accumulation in the NVSwitch; one fp16 rounding per hop in NCCL) - half the bytes,
+                                   and an error of up to half an fp16 ulp of every partial sum on top of the final rounding;
+                                   EFA_WIRE_F32 = the fp32 accumulators are summed (the reference's types, run_drivers.cu:26-30)
+                                   and the sum is rounded once into the fp16 output. EFA_WIRE_AUTO = fp32. */
+    int debug_target_bias;      /* test hook, 0 in normal use: added on the HOST to the counter target that stream mode's
+                                   consumers wait for (the cuStreamWaitValue32 of the projection stream, the polling of
+                                   the persistent kernel), so that a guarded wait runs out and its recovery can be
+                                   tested without any fault on the GPU */
     efa_flash_params flash_tc;
 } efa_params;
 
@@ -223,6 +243,14 @@ typedef struct efa_ctx efa_ctx;   /* RunCtx (attn_defs.cuh:86-99): streams, comm
  * `prioritize`), ncomm NCCL communicators over the world's ranks. Collective over the world. */
 int efa_make_ctx(efa_ctx** out, const efa_world* world, int ncomm, int prioritize);
 int efa_destroy_ctx(efa_ctx* ctx);
+
+/* Output buffer for efa_run_mode with EFA_REDUCE_NVLS that the reduction can write in place: a pointer into this
+ * rank's memory of the context's multicast region (fp16 [S][d]; valid until the context is destroyed or a larger
+ * problem makes the region grow). The switch stores the reduced rows straight into every rank's buffer. With any
+ * other output pointer the reduced rows are copied there from the region by one device-to-device copy per
+ * reduction. Collective (it may create the region). The reference's callers allocate the output themselves
+ * (attn_bench.cu:135-136); this is the counterpart of NCCL's registered user buffers and has none there. */
+int efa_nvls_output(efa_ctx* ctx, const efa_params* p, void** output);
 
 /* Limits of the waits that guard against a signal that never comes (the reference has none: a wrong counter
  * target blocks its cuStreamWaitValue32 forever, run_drivers.cu:228-230). device_ms: how long a kernel of this

@@ -33,9 +33,13 @@ def test_two_calls_in_a_row_match_the_ordinary_entry_point(pkg, oracle, torch_cu
     torch = torch_cuda
     calls = [
         # S, d, H, split, causal, seed, q_start, q_rows, dtype
-        (1024, 512, 8, 4, 1, 42, 256, 768, pkg.F16),
-        (512, 256, 4, 2, 0, 123, 128, 320, pkg.F32),
+        (1024, 512, 8, 4, 1, 42, 256, 768, pkg.F16),        # d_h = 64
+        (512, 256, 4, 2, 0, 123, 128, 320, pkg.F32),        # d_h = 64, fp32 O
+        (512, 256, 4, 1, 1, 7, 64, 448, pkg.F16),           # split = 1: no partials, O written directly
+        (1024, 1024, 8, 2, 1, 9, 0, 512, pkg.F16),          # d_h = 128
+        (256, 64, 4, 2, 0, 11, 0, 256, pkg.F32),            # d_h = 16
     ]
+    pkg.flash_attn_tc_noalloc_status(reset=True)
     for S, d, H, split, causal, seed, q_start, q_rows, o_dtype in calls:
         p = pkg.make_params(S, d, H, 64, 2, split, causal)
         bits, vals = ref_inputs_f16(oracle, S, d, H, 1, 0, seed)
@@ -45,6 +49,7 @@ def test_two_calls_in_a_row_match_the_ordinary_entry_point(pkg, oracle, torch_cu
         got = torch.full((q_rows, p.d_local), float("nan"), dtype=tdtype, device="cuda")
         pkg.flash_attn_tc_forward_noalloc(dev[0], dev[1], dev[2], got, q_start, q_rows, p.flash_tc, None, o_dtype)
         torch.cuda.synchronize()
+        assert pkg.flash_attn_tc_noalloc_status()[0] == 0, pkg.flash_attn_tc_noalloc_status()
         g, w = got.float().cpu().numpy(), want.float().cpu().numpy()
         assert np.isfinite(g).all()
         diff = float(np.abs(g - w).max())
