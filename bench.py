@@ -263,8 +263,10 @@ def main():
     qkv_shape = (p.H_local, p.S, p.d_h)
     host = [torch.empty(qkv_shape, dtype=torch.float16).pin_memory() for _ in range(3)]
     host.append(torch.empty((p.d_local, p.d), dtype=torch.float16).pin_memory())
-    # The reduced result is identical on every rank: rank 0 reads it back, the others pass no host buffer.
-    host_out = torch.empty((p.S, p.d), dtype=torch.float16).pin_memory() if rank == 0 else None
+    # The reduced result is identical on every rank: each rank reads back its own share of the rows (S / N of them)
+    # over its own PCIe link, so that every row reaches host memory exactly once.
+    share = p.S // world_size
+    host_out = torch.empty((share, p.d), dtype=torch.float16).pin_memory()
     pkg.fill_host_inputs(p, rank, 42, pkg.RECIPE_NORMAL, *host)
     dev = [h.cuda() for h in host]
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")      # > 126 MB L2
@@ -289,7 +291,7 @@ def main():
         flush.fill_(rank + 1)                   # evict L2 between steps
         barrier()
         if host_path:
-            return pkg.run_mode_host(ctx, mode, *host, host_out, p)
+            return pkg.run_mode_host(ctx, mode, *host, host_out, p, out_row0=rank * share, out_rows=share)
         return pkg.run_mode(ctx, mode, weights, out, p)
 
     pkg.kernel_status_reset()
@@ -348,8 +350,8 @@ def main():
     for _ in range(2):
         one_step(host_path=True)
     e2e_ms = statistics.mean([one_step(host_path=True).wall_ms for _ in range(max(3, min(args.steps, 10)))])
-    h2d = sum(h.numel() * 2 for h in host)
-    d2h = p.S * p.d * 2                          # rank 0's copy-out; the other ranks copy nothing out
+    h2d = sum(h.numel() * 2 for h in host) * world_size      # every rank copies its own Q, K, V and W_O slice in
+    d2h = p.S * p.d * 2                                       # the result once, S / N rows per rank
 
     pk = measured_peaks()
     fl = attention_flops(p.S, p.d_h, p.H_local, p.causal)
@@ -372,8 +374,9 @@ def main():
                         mode=args.mode, split=p.split, reduce=args.reduce, wire=args.wire, row_order=args.order,
                         group_tiles=args.group_tiles or "auto (S/8 rows per launch)",
                         l2="256 MB buffer written between steps",
-                        e2e="pinned host Q/K/V/W_O copied in by every rank, fp16 [S][d] result copied out by rank 0 (it is "
-                            "identical on all ranks); copy-in, compute and copy-out pipelined over row chunks",
+                        e2e="pinned host Q/K/V/W_O copied in by every rank, the fp16 [S][d] result (identical on all ranks) copied "
+                            "out once, S/N rows by each rank; copy-in, compute and copy-out pipelined over row chunks; bytes "
+                            "are totals over the ranks",
                         inputs="Q,K,V ~ N(0,1) fp16 [H_local][S][d_h]; W_O ~ N(0,1/d) fp16; seed 42"),
             tokens_per_s=p.S / (ms * 1e-3),
             modes_ms=modes, modes_ms_proj_f32=modes_f32, exposed_comm_frac=exposed,

@@ -121,6 +121,8 @@ _SIGNATURES = {
                                         C.POINTER(RunStats)]),
     "efa_run_mode_host": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                     C.c_void_p, C.POINTER(Params), C.POINTER(RunStats)]),
+    "efa_run_mode_host_rows": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                         C.c_void_p, C.c_int, C.c_int, C.POINTER(Params), C.POINTER(RunStats)]),
 }
 EXPORTED_SYMBOLS = tuple(_SIGNATURES)
 
@@ -425,9 +427,13 @@ def run_mode_residual(ctx: Ctx, mode: int, w: Weights, residual, output, p: Para
     return st
 
 
-def run_mode_host(ctx: Ctx, mode: int, Qh, Kh, Vh, W_O, output, p: Params) -> RunStats:
-    """The block on host buffers (copies inside the timed region)."""
+def run_mode_host(ctx: Ctx, mode: int, Qh, Kh, Vh, W_O, output, p: Params, out_row0: int = 0,
+                  out_rows: Optional[int] = None) -> RunStats:
+    """The block on host buffers (copies inside the timed region). ``output`` receives rows
+    [out_row0, out_row0 + out_rows) of the result (all of them by default; None: nothing is copied back)."""
     st = RunStats()
-    _check(lib().efa_run_mode_host(ctx.handle, mode, _ptr(Qh), _ptr(Kh), _ptr(Vh), _ptr(W_O), _ptr(output),
-                                   C.byref(p), C.byref(st)), "run_mode_host")
+    if out_rows is None:
+        out_rows = p.S - out_row0 if output is not None else 0
+    _check(lib().efa_run_mode_host_rows(ctx.handle, mode, _ptr(Qh), _ptr(Kh), _ptr(Vh), _ptr(W_O), _ptr(output),
+                                        out_row0, out_rows, C.byref(p), C.byref(st)), "run_mode_host")
     return st

@@ -111,15 +111,21 @@ extern "C" int efa_run_mode_residual(efa_ctx* ctx, int mode, const efa_weights* 
     return run_mode_impl(ctx, mode, *w, output, *p, stats, residual);
 }
 
-extern "C" int efa_run_mode_host(efa_ctx* c, int mode,
-                                 const uint16_t* Qh, const uint16_t* Kh, const uint16_t* Vh, const uint16_t* W_O,
-                                 uint16_t* output, const efa_params* p, efa_run_stats* stats)
+extern "C" int efa_run_mode_host_rows(efa_ctx* c, int mode,
+                                      const uint16_t* Qh, const uint16_t* Kh, const uint16_t* Vh, const uint16_t* W_O,
+                                      uint16_t* output, int out_row0, int out_rows, const efa_params* p, efa_run_stats* stats)
 {
     if (!c || !Qh || !Kh || !Vh || !W_O || !p) { set_error("efa_run_mode_host: null argument"); return 2; }
     if (p->proj_f32) { set_error("efa_run_mode_host: the host-buffer path returns fp16 (proj_f32 must be 0)"); return 2; }
+    if (!output) out_rows = 0;
+    if (out_rows < 0 || out_row0 < 0 || (out_rows > 0 && out_row0 + out_rows > p->S)) {
+        set_error("efa_run_mode_host: rows [%d, %d) are outside the result", out_row0, out_row0 + out_rows);
+        return 2;
+    }
     const size_t qkv = (size_t)p->H_local * p->S * p->d_h * 2;
     const size_t wb = (size_t)p->d_local * p->d * 2;
-    const size_t ob = (size_t)p->S * p->d * 2;
+    const size_t rowb = (size_t)p->d * 2;
+    const size_t ob = (size_t)p->S * rowb;
     {
         size_t a = c->h_qkv_bytes, b = c->h_qkv_bytes, d = c->h_qkv_bytes;
         const bool fresh = a < qkv || !c->h_Q || !c->h_K || !c->h_V;
@@ -132,12 +138,17 @@ extern "C" int efa_run_mode_host(efa_ctx* c, int mode,
             EFA_CUDA(cudaMemset(c->h_V, 0, d));
         }
         c->h_qkv_bytes = a < b ? (a < d ? a : d) : (b < d ? b : d);
-        if (ensure_bytes(&c->h_W, &c->h_w_bytes, wb) || ensure_bytes(&c->h_out, &c->h_out_bytes, ob)) return 1;
+        if (ensure_bytes(&c->h_W, &c->h_w_bytes, wb)) return 1;
     }
-    if (mode == EFA_MODE_STREAM && p->causal && !p->skip_proj && p->reduce == EFA_REDUCE_NCCL) {
+    // Device result: the multicast region's result buffer when the switch reduces (written in place), else staging.
+    void* dev_out = nullptr;
+    const bool nvls = p->reduce == EFA_REDUCE_NVLS && p->R > 1 && !p->skip_comm;
+    if (nvls) { if (efa_nvls_output(c, p, &dev_out)) return 1; }
+    else { if (ensure_bytes(&c->h_out, &c->h_out_bytes, ob)) return 1; dev_out = c->h_out; }
+    if (mode == EFA_MODE_STREAM && p->causal && !p->skip_proj && p->reduce != EFA_REDUCE_P2P) {
         // copy-in, compute and copy-out overlap chunk by chunk
         efa_weights dev{c->h_Q, c->h_K, c->h_V, c->h_W};
-        return run_stream_host_pipelined(c, Qh, Kh, Vh, W_O, output, dev, c->h_out, *p, stats);
+        return run_stream_host_pipelined(c, Qh, Kh, Vh, W_O, output, out_row0, out_rows, dev, dev_out, *p, stats);
     }
     if (world_barrier(c->world)) return 1;
     const auto t0 = std::chrono::steady_clock::now();
@@ -150,15 +161,23 @@ extern "C" int efa_run_mode_host(efa_ctx* c, int mode,
     efa_weights w{c->h_Q, c->h_K, c->h_V, c->h_W};
     efa_run_stats inner;
     std::memset(&inner, 0, sizeof(inner));
-    if (run_mode_impl(c, mode, w, c->h_out, *p, &inner)) return 1;
-    if (output && mode != EFA_MODE_ATTN && mode != EFA_MODE_ATTN_TILED) {
-        EFA_CUDA(cudaMemcpyAsync(output, c->h_out, ob, cudaMemcpyDeviceToHost, s));
+    if (run_mode_impl(c, mode, w, dev_out, *p, &inner)) return 1;
+    if (out_rows > 0 && mode != EFA_MODE_ATTN && mode != EFA_MODE_ATTN_TILED) {
+        EFA_CUDA(cudaMemcpyAsync(output, static_cast<char*>(dev_out) + (size_t)out_row0 * rowb, (size_t)out_rows * rowb,
+                                 cudaMemcpyDeviceToHost, s));
         EFA_CUDA(cudaStreamSynchronize(s));
     }
     double ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
     if (world_max(c->world, &ms)) return 1;
     if (stats) { *stats = inner; stats->wall_ms = ms; }
     return 0;
+}
+
+extern "C" int efa_run_mode_host(efa_ctx* c, int mode,
+                                 const uint16_t* Qh, const uint16_t* Kh, const uint16_t* Vh, const uint16_t* W_O,
+                                 uint16_t* output, const efa_params* p, efa_run_stats* stats)
+{
+    return efa_run_mode_host_rows(c, mode, Qh, Kh, Vh, W_O, output, 0, (output && p) ? p->S : 0, p, stats);
 }
 
 extern "C" int efa_world_selftest(const efa_world* w)

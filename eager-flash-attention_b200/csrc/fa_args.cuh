@@ -20,6 +20,7 @@ struct FaArgs {
     int     tile_rows;
     int*    status;
     int     band_blocks;    // two-tile kernel: 256-row blocks per band of the work order (0 or 1 = strict row order)
+    int     counters_sys;   // the tile counters live in host memory: order the rows before the count at system scope
     int     heavy_first;    // two-tile kernel: take the row blocks (or bands) from the last to the first; with a causal
                             // mask the last rows sweep the most keys, so the longest items start first
 };

@@ -308,7 +308,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ,
 
     // ---- signal tile completion: one count per finished 64-row block, after the rows are visible
     if (!failed && a.tile_counters != nullptr) {
-        __threadfence();
+        if (a.counters_sys) __threadfence_system(); else __threadfence();
         __syncthreads();
         if (tid == 0) {
             for (int sb = 0; sb < rows_valid; sb += 64)
@@ -501,6 +501,13 @@ int fa_forward(const void* Q, const void* K, const void* V, void* O, int o_dtype
     a.nsplit = p.split; a.kv_len = p.S / p.split; a.causal = p.causal;
     a.scale_log2e = p.scale * 1.4426950408889634f;
     a.tile_counters = tile_counters; a.tile_rows = tile_rows;
+    a.counters_sys = 0;
+    if (tile_counters != nullptr) {
+        // Counters in (mapped) host memory are read over PCIe by whoever waits for them: fence at system scope then.
+        cudaPointerAttributes attr;
+        if (cudaPointerGetAttributes(&attr, tile_counters) == cudaSuccess) a.counters_sys = attr.type == cudaMemoryTypeHost ? 1 : 0;
+        else (void)cudaGetLastError();
+    }
     a.status = kernel_status_word();
     a.band_blocks = (tile_counters == nullptr) ? (q_rows + 255) / 256 : band_rows / 256;
     // Nobody waits for particular rows of a launch without counters, so under a causal mask its longest work
@@ -645,6 +652,7 @@ int fa_forward_noalloc(const void* Q, const void* K, const void* V, void* O, int
     a.nsplit = p.split; a.kv_len = p.S / p.split; a.causal = p.causal;
     a.scale_log2e = p.scale * 1.4426950408889634f;
     a.tile_counters = nullptr; a.tile_rows = 0;
+    a.counters_sys = 0;
     a.status = status;                       // a word of the module, see noalloc_status()
     a.band_blocks = 0;
     a.heavy_first = 0;

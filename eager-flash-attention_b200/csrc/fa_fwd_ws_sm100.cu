@@ -511,12 +511,12 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ,
                 // ---- completion signal: one count per finished 64-row block, after its rows are visible.
                 // A 64-row block is two warps; the second of them to get here publishes the count.
                 if (a.tile_counters != nullptr) {
-                    __threadfence();
+                    if (a.counters_sys) __threadfence_system(); else __threadfence();
                     __syncwarp();
                     if (lane == 0) {
                         const int half = (warp & 3) >> 1;
                         if (atomicAdd(&half_done[q][half], 1) == 1) {
-                            __threadfence();
+                            if (a.counters_sys) __threadfence_system(); else __threadfence();
                             atomicAdd(a.tile_counters + (block_row0 + q * WS_BM + half * 64) / a.tile_rows, 1);
                         }
                     }

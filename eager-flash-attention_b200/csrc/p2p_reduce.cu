@@ -490,46 +490,63 @@ int p2p_prepare(efa_ctx* c, const efa_params& p, void* output)
     const size_t stage_bytes = (size_t)nrb * NB * 128 * 128 * sizeof(__half);
     const size_t nflags = (size_t)2 * nrb;          // arrive[nrb] then done[nrb]
     (void)NBR;
-    if (R > 1) EFA_CUDA(cudaMalloc(&st->stage, stage_bytes));
-    EFA_CUDA(cudaMalloc(&st->flags, nflags * sizeof(int)));
-    EFA_CUDA(cudaMemset(st->flags, 0, nflags * sizeof(int)));
-    EFA_CUDA(cudaMalloc(&st->counters, (size_t)p.num_tiles * sizeof(int)));
-    EFA_CUDA(cudaMemset(st->counters, 0, (size_t)p.num_tiles * sizeof(int)));
-    EFA_CUDA(cudaDeviceSynchronize());
+    // The rebuild is collective. A failure on one rank (no memory, an export or an import that fails) must not leave
+    // the others inside the next exchange, so every local result is folded into a word that all ranks agree on
+    // before anyone returns.
+    auto agreed = [&](bool mine_ok) {
+        double v = mine_ok ? 0.0 : 1.0;
+        if (world_max(c->world, &v)) return false;
+        return v == 0.0;
+    };
+    bool ok = true;
+    if (R > 1) ok = cudaMalloc(&st->stage, stage_bytes) == cudaSuccess;
+    ok = ok && cudaMalloc(&st->flags, nflags * sizeof(int)) == cudaSuccess &&
+         cudaMemset(st->flags, 0, nflags * sizeof(int)) == cudaSuccess &&
+         cudaMalloc(&st->counters, (size_t)p.num_tiles * sizeof(int)) == cudaSuccess &&
+         cudaMemset(st->counters, 0, (size_t)p.num_tiles * sizeof(int)) == cudaSuccess &&
+         cudaDeviceSynchronize() == cudaSuccess;
+    if (!ok) (void)cudaGetLastError();
+    if (!agreed(ok)) { release(st); set_error("reduce=p2p: a rank could not allocate its staging buffers"); return 1; }
     for (int r = 0; r < 8; r++) { st->stage_peer[r] = nullptr; st->flags_peer[r] = nullptr; st->out_peer[r] = nullptr; }
     st->stage_peer[rank] = st->stage; st->flags_peer[rank] = st->flags; st->out_peer[rank] = static_cast<__half*>(output);
 
     if (R > 1) {
-        if (!c->world.allgather_bytes) { set_error("reduce=p2p needs the world's allgather_bytes callback"); return 2; }
+        if (!c->world.allgather_bytes) { release(st); set_error("reduce=p2p needs the world's allgather_bytes callback"); return 2; }
         const DriverApi* api = driver_api();
-        if (!api) return 1;
         IpcPacket mine;
         std::memset(&mine, 0, sizeof(mine));
-        mine.ok = 1;
+        mine.ok = api ? 1 : 0;
         CUdeviceptr base = 0; size_t range = 0;
-        if (api->cuMemGetAddressRange(&base, &range, (CUdeviceptr)output) != CUDA_SUCCESS) mine.ok = 0;
+        if (mine.ok && api->cuMemGetAddressRange(&base, &range, (CUdeviceptr)output) != CUDA_SUCCESS) mine.ok = 0;
         if (mine.ok && cudaIpcGetMemHandle(&mine.out, (void*)base) != cudaSuccess) mine.ok = 0;
         mine.out_offset = (unsigned long long)((CUdeviceptr)output - base);
         if (mine.ok && cudaIpcGetMemHandle(&mine.stage, st->stage) != cudaSuccess) mine.ok = 0;
         if (mine.ok && cudaIpcGetMemHandle(&mine.flags, st->flags) != cudaSuccess) mine.ok = 0;
         if (!mine.ok) (void)cudaGetLastError();
         std::vector<IpcPacket> all(R);
-        if (c->world.allgather_bytes(c->world.user, &mine, all.data(), sizeof(IpcPacket))) { set_error("reduce=p2p: handle exchange failed"); return 1; }
+        if (c->world.allgather_bytes(c->world.user, &mine, all.data(), sizeof(IpcPacket))) { release(st); set_error("reduce=p2p: handle exchange failed"); return 1; }
         for (int r = 0; r < R; r++)
-            if (!all[r].ok) { set_error("reduce=p2p: rank %d could not export its buffers over CUDA IPC (is the output a cudaMalloc allocation?)", r); return 5; }
-        for (int r = 0; r < R; r++) {
+            if (!all[r].ok) {
+                release(st);
+                set_error("reduce=p2p: rank %d could not export its buffers over CUDA IPC (is the output a cudaMalloc allocation?)", r);
+                return 5;
+            }
+        bool opened = true;
+        for (int r = 0; r < R && opened; r++) {
             if (r == rank) continue;
             void* ps = nullptr; void* pf = nullptr; void* po = nullptr;
-            EFA_CUDA(cudaIpcOpenMemHandle(&ps, all[r].stage, cudaIpcMemLazyEnablePeerAccess));
-            st->opened.push_back(ps);
-            EFA_CUDA(cudaIpcOpenMemHandle(&pf, all[r].flags, cudaIpcMemLazyEnablePeerAccess));
-            st->opened.push_back(pf);
-            EFA_CUDA(cudaIpcOpenMemHandle(&po, all[r].out, cudaIpcMemLazyEnablePeerAccess));
-            st->opened.push_back(po);
-            st->stage_peer[r] = static_cast<__half*>(ps);
-            st->flags_peer[r] = static_cast<int*>(pf);
-            st->out_peer[r] = reinterpret_cast<__half*>(static_cast<char*>(po) + all[r].out_offset);
+            opened = cudaIpcOpenMemHandle(&ps, all[r].stage, cudaIpcMemLazyEnablePeerAccess) == cudaSuccess;
+            if (opened) { st->opened.push_back(ps); opened = cudaIpcOpenMemHandle(&pf, all[r].flags, cudaIpcMemLazyEnablePeerAccess) == cudaSuccess; }
+            if (opened) { st->opened.push_back(pf); opened = cudaIpcOpenMemHandle(&po, all[r].out, cudaIpcMemLazyEnablePeerAccess) == cudaSuccess; }
+            if (opened) {
+                st->opened.push_back(po);
+                st->stage_peer[r] = static_cast<__half*>(ps);
+                st->flags_peer[r] = static_cast<int*>(pf);
+                st->out_peer[r] = reinterpret_cast<__half*>(static_cast<char*>(po) + all[r].out_offset);
+            }
         }
+        if (!opened) (void)cudaGetLastError();
+        if (!agreed(opened)) { release(st); set_error("reduce=p2p: a rank could not map a peer's buffers (cudaIpcOpenMemHandle)"); return 5; }
         if (world_barrier(c->world)) return 1;
     }
     st->S = p.S; st->d = p.d; st->d_local = p.d_local; st->R = R; st->tile = p.tile; st->target = target;

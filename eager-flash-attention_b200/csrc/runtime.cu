@@ -374,7 +374,8 @@ extern "C" int efa_destroy_ctx(efa_ctx* c)
     for (cudaEvent_t e : c->events) cudaEventDestroy(e);
     for (cudaEvent_t e : c->trace_events) cudaEventDestroy(e);
     for (cudaEvent_t e : {c->ev_t0, c->ev_t1, c->ev_t2, c->ev_t3}) if (e) cudaEventDestroy(e);
-    for (void* q : {c->O_all, c->send_buf, (void*)c->counters, (void*)c->ws_O, (void*)c->ws_m, (void*)c->ws_l,
+    if (c->counters) cudaFreeHost(c->counters);
+    for (void* q : {c->O_all, c->send_buf, (void*)c->ws_O, (void*)c->ws_m, (void*)c->ws_l,
                     c->h_Q, c->h_K, c->h_V, c->h_W, c->h_out})
         if (q) cudaFree(q);
     delete c;

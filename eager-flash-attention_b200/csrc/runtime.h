@@ -24,7 +24,7 @@ struct efa_ctx {
     // Scratch, grown on demand and reused across run_mode calls (freed by efa_destroy_ctx).
     void*  O_all = nullptr;     size_t O_all_bytes = 0;      // fp16 [S][d_local]
     void*  send_buf = nullptr;  size_t send_bytes = 0;       // fp16 [S][d]
-    int*   counters = nullptr;  size_t counters_n = 0;
+    int*   counters = nullptr;  size_t counters_n = 0;       // mapped pinned host memory: the host can always release a wait
     float* ws_O = nullptr; float* ws_m = nullptr; float* ws_l = nullptr;
     size_t ws_O_n = 0, ws_ml_n = 0;
     std::vector<cudaEvent_t> events;                        // disable-timing events, one per tile + a few
@@ -61,10 +61,12 @@ int ensure_trace_events(efa_ctx* c, size_t n);
 int run_mode_impl(efa_ctx* c, int mode, const efa_weights& w, void* output, const efa_params& p, efa_run_stats* stats,
                   const void* residual = nullptr);
 
-// Stream mode on HOST buffers as a pipeline over row chunks (causal, split == 1): the copy-in of chunk c+1,
-// the attention / projection / AllReduce of chunk c and the copy-out of chunk c-1 overlap. `dev` holds the
-// device staging of Q, K, V, W_O; `dev_out` the device output. Returns 0 and fills stats->wall_ms (max over ranks).
+// Stream mode on HOST buffers as a pipeline over row chunks (causal): the copy-in of chunk c+1, the attention /
+// projection / reduction of chunk c and the copy-out of chunk c-1 overlap. `dev` holds the device staging of Q, K, V,
+// W_O; `dev_out` the device output. host_out receives rows [out_row0, out_row0 + out_rows) of the result (nothing when
+// out_rows == 0). Returns 0 and fills stats->wall_ms (max over ranks).
 int run_stream_host_pipelined(efa_ctx* c, const uint16_t* Qh, const uint16_t* Kh, const uint16_t* Vh, const uint16_t* W_O,
-                              uint16_t* host_out, const efa_weights& dev, void* dev_out, const efa_params& p, efa_run_stats* stats);
+                              uint16_t* host_out, int out_row0, int out_rows, const efa_weights& dev, void* dev_out,
+                              const efa_params& p, efa_run_stats* stats);
 
 }  // namespace efa

@@ -11,6 +11,7 @@
 #include "nvls_reduce.h"
 #include "p2p_reduce.h"
 
+#include <algorithm>
 #include <chrono>
 #include <cstdio>
 #include <cstring>
@@ -164,34 +165,41 @@ struct Run {
     }
 };
 
-// Wait for a stream with a deadline. When the deadline passes (a tile counter that never reaches
-// its target would block cuStreamWaitValue32 forever), the counters are overwritten with a large
-// value from another stream so that every pending wait is released, and an error is returned.
+// Wait for a stream with a deadline. When the deadline passes (a tile counter that never reaches its target would
+// block cuStreamWaitValue32 forever), the HOST stores a value above every target into the counters, which live in
+// mapped pinned host memory for exactly this reason: the release must not depend on another stream getting through
+// the GPU's front end, where it can sit in the same hardware queue behind the very wait it is meant to release
+// (measured: a memset from a second stream did not get through). Then the stream is given the same time again to
+// drain, and an error is returned either way.
 int sync_stream(efa_ctx* c, cudaStream_t s, int* counters, size_t ncounters)
 {
     const double deadline_ms = c->host_wait_limit_ms;
-    const double t0 = now_ms();
-    long spins = 0;
-    while (true) {
-        cudaError_t e = cudaStreamQuery(s);
-        if (e == cudaSuccess) return 0;
-        if (e != cudaErrorNotReady) return check_cuda(e, "cudaStreamQuery", __FILE__, __LINE__);
-        if ((++spins & 1023) == 0) {
-            const double el = now_ms() - t0;
-            if (el > deadline_ms) break;
-            if (el > 2000.0) std::this_thread::sleep_for(std::chrono::microseconds(200));
+    auto poll = [&](double limit_ms) -> int {        // 0 done, 1 not ready in time, 2 error
+        const double t0 = now_ms();
+        long spins = 0;
+        while (true) {
+            cudaError_t e = cudaStreamQuery(s);
+            if (e == cudaSuccess) return 0;
+            if (e != cudaErrorNotReady) { check_cuda(e, "cudaStreamQuery", __FILE__, __LINE__); return 2; }
+            if ((++spins & 1023) == 0) {
+                const double el = now_ms() - t0;
+                if (el > limit_ms) return 1;
+                if (el > 2000.0) std::this_thread::sleep_for(std::chrono::microseconds(200));
+            }
         }
-    }
+    };
+    const int first = poll(deadline_ms);
+    if (first == 0) return 0;
+    if (first == 2) return 1;
+    bool drained = false;
     if (counters && ncounters) {
-        cudaStream_t rescue;
-        if (cudaStreamCreateWithFlags(&rescue, cudaStreamNonBlocking) == cudaSuccess) {
-            cudaMemsetAsync(counters, 0x7f, ncounters * sizeof(int), rescue);
-            cudaStreamSynchronize(rescue);
-            cudaStreamDestroy(rescue);
-        }
-        cudaStreamSynchronize(s);            // nothing on it waits for a counter any more
+        volatile int* host = counters;               // the same words the front end polls (unified addressing)
+        for (size_t i = 0; i < ncounters; i++) host[i] = 0x7f7f7f7f;
+        __sync_synchronize();
+        drained = poll(deadline_ms) == 0;
     }
-    set_error("stream did not finish within %.1f s; pending tile waits were released", deadline_ms / 1e3);
+    set_error("stream did not finish within %.1f s; pending tile waits were released%s", deadline_ms / 1e3,
+              drained ? "" : " but the stream has not drained");
     return 4;
 }
 
@@ -223,10 +231,15 @@ int scratch(efa_ctx* c, const Run& r, size_t o_rows, size_t send_rows, size_t nc
     if (o_rows && ensure_bytes(&c->O_all, &c->O_all_bytes, o_rows * p.d_local * sizeof(__half))) return 1;
     if (r.nvls()) { if (nvls_prepare(c, p)) return 1; }
     else if (send_rows && ensure_bytes(&c->send_buf, &c->send_bytes, send_rows * r.send_row_bytes())) return 1;
-    if (ncounters) {
-        size_t have = c->counters_n * sizeof(int);
-        if (ensure_bytes((void**)&c->counters, &have, ncounters * sizeof(int))) return 1;
-        c->counters_n = have / sizeof(int);
+    if (ncounters > c->counters_n) {
+        // Tile counters: mapped pinned host memory (see sync_stream). The attention kernel adds to them with
+        // fire-and-forget reductions over PCIe, the front end polls them for cuStreamWaitValue32.
+        if (c->counters) { EFA_CUDA(cudaFreeHost(c->counters)); c->counters = nullptr; c->counters_n = 0; }
+        void* hp = nullptr;
+        EFA_CUDA(cudaHostAlloc(&hp, ncounters * sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable));
+        std::memset(hp, 0, ncounters * sizeof(int));
+        c->counters = static_cast<int*>(hp);
+        c->counters_n = ncounters;
     }
     if (p.split > 1 && ws_rows) {
         size_t haveO = c->ws_O_n * sizeof(float);
@@ -367,7 +380,6 @@ int run_stream(Run& r, char* output, efa_run_stats* st)
     char* send_buf = r.send_base();
     int* counters = c->counters;
     const int target = efa_blocks_per_tile(&p) + p.debug_target_bias;
-    cudaEvent_t reset_done = c->events[p.num_tiles];
     const bool fused = (p.reduce == EFA_REDUCE_P2P) && !p.skip_comm && !p.skip_proj;
     // Launch plan (efa_stream_plan): groups of consecutive tiles per projection + reduction launch in the order in
     // which they complete, and the band of rows within which the attention kernel may reorder its work (better
@@ -408,8 +420,9 @@ int run_stream(Run& r, char* output, efa_run_stats* st)
     if (world_barrier(c->world)) return 1;
     const double t0 = now_ms();
 
-    EFA_CUDA(cudaMemsetAsync(counters, 0, (size_t)p.num_tiles * sizeof(int), c->compute_stream));
-    EFA_CUDA(cudaEventRecord(reset_done, c->compute_stream));
+    // Counters start at zero: a host store (the previous run was waited for on every stream, and the front end reads
+    // these words only after the waits below are enqueued).
+    std::memset(counters, 0, (size_t)p.num_tiles * sizeof(int));
     // p.reserve_sms = k runs the attention kernel in its persistent form on (SMs - k) CTAs, so that the
     // projection and the reduction of finished tiles always find an SM. Measured on 8 GPUs (benchmark
     // shape) this loses: the projection of a group is then confined to the k reserved SMs, while with the
@@ -418,7 +431,6 @@ int run_stream(Run& r, char* output, efa_run_stats* st)
     if (r.attention_raw(O_all, p.S, 0, p.S, c->compute_stream, counters, p.tile, p.reserve_sms, band_rows, 0, descending)) return 1;
     EFA_CUDA(cudaEventRecord(c->ev_t1, c->compute_stream));
 
-    EFA_CUDA(cudaStreamWaitEvent(c->proj_stream, reset_done, 0));   // never observe a stale counter
     // Tiles are signalled one by one; the projection and the reduction are launched once per group of
     // consecutive tiles, after a front-end wait on every counter of the group. group_tiles = 1 is the
     // reference's schedule. Small tiles make one launch and one collective per tile cost more than the
@@ -426,12 +438,10 @@ int run_stream(Run& r, char* output, efa_run_stats* st)
     // eight GPUs), so the default groups about S/8 rows.
     // From here on an error must not leave front-end waits behind on the projection stream: `fail` releases them.
     auto fail = [&]() {
-        cudaStream_t rescue;
-        if (cudaStreamCreateWithFlags(&rescue, cudaStreamNonBlocking) == cudaSuccess) {
-            cudaMemsetAsync(counters, 0x7f, (size_t)p.num_tiles * sizeof(int), rescue);
-            cudaStreamSynchronize(rescue);
-            cudaStreamDestroy(rescue);
-        }
+        cudaStreamSynchronize(c->compute_stream);                 // the attention kernel no longer touches the counters
+        volatile int* host = counters;
+        for (int i = 0; i < p.num_tiles; i++) host[i] = 0x7f7f7f7f;
+        __sync_synchronize();
         cudaStreamSynchronize(c->proj_stream);
         return 1;
     };
@@ -496,7 +506,8 @@ int run_comm_only(Run& r, char* output, efa_run_stats* st)
 }  // namespace
 
 int run_stream_host_pipelined(efa_ctx* c, const uint16_t* Qh, const uint16_t* Kh, const uint16_t* Vh, const uint16_t* W_O,
-                              uint16_t* host_out, const efa_weights& dev, void* dev_out, const efa_params& p, efa_run_stats* stats)
+                              uint16_t* host_out, int out_row0, int out_rows, const efa_weights& dev, void* dev_out,
+                              const efa_params& p, efa_run_stats* stats)
 {
     const DriverApi* api = driver_api();
     if (!api) return 1;
@@ -521,16 +532,14 @@ int run_stream_host_pipelined(efa_ctx* c, const uint16_t* Qh, const uint16_t* Kh
     auto ev_in = [&](int i) { return c->events[3 * i]; };
     auto ev_proj = [&](int i) { return c->events[3 * i + 1]; };
     auto ev_ar = [&](int i) { return c->events[3 * i + 2]; };
-    cudaEvent_t ev_w = c->events[3 * nchunk], reset_done = c->events[3 * nchunk + 1];
+    cudaEvent_t ev_w = c->events[3 * nchunk];
     const size_t head_pitch = (size_t)p.S * p.d_h * 2;            // bytes between heads, host and device alike
 
     if (world_barrier(c->world)) return 1;
     const double t0 = now_ms();
     EFA_CUDA(cudaMemcpyAsync(dev.W_O, W_O, (size_t)p.d_local * p.d * 2, cudaMemcpyHostToDevice, c->h2d_stream));
     EFA_CUDA(cudaEventRecord(ev_w, c->h2d_stream));
-    EFA_CUDA(cudaMemsetAsync(counters, 0, (size_t)p.num_tiles * sizeof(int), c->compute_stream));
-    EFA_CUDA(cudaEventRecord(reset_done, c->compute_stream));
-    EFA_CUDA(cudaStreamWaitEvent(c->proj_stream, reset_done, 0));
+    std::memset(counters, 0, (size_t)p.num_tiles * sizeof(int));
     EFA_CUDA(cudaStreamWaitEvent(c->proj_stream, ev_w, 0));
     for (int i = 0; i < nchunk; i++) {
         const int t0c = i * ct, nt = (t0c + ct <= p.num_tiles) ? ct : p.num_tiles - t0c;
@@ -561,9 +570,11 @@ int run_stream_host_pipelined(efa_ctx* c, const uint16_t* Qh, const uint16_t* Kh
                                      cudaMemcpyDeviceToDevice, c->comm_streams[slot]));
         } else if (r.allreduce(slot, send_buf + (size_t)row0 * sb, output + (size_t)row0 * rb, (size_t)rows * p.d)) return 1;
         EFA_CUDA(cudaEventRecord(ev_ar(i), c->comm_streams[slot]));
-        if (host_out) {
+        // the part of this chunk that the caller wants on the host
+        const int lo = std::max(row0, out_row0), hi = std::min(row0 + rows, out_row0 + out_rows);
+        if (host_out && hi > lo) {
             EFA_CUDA(cudaStreamWaitEvent(c->d2h_stream, ev_ar(i), 0));
-            EFA_CUDA(cudaMemcpyAsync(host_bytes + (size_t)row0 * rb, output + (size_t)row0 * rb, (size_t)rows * rb,
+            EFA_CUDA(cudaMemcpyAsync(host_bytes + (size_t)(lo - out_row0) * rb, output + (size_t)lo * rb, (size_t)(hi - lo) * rb,
                                      cudaMemcpyDeviceToHost, c->d2h_stream));
         }
     }

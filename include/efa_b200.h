@@ -301,12 +301,21 @@ int efa_run_mode_residual(efa_ctx* ctx, int mode, const efa_weights* w, const vo
 /* The whole block on HOST buffers: copies this rank's fp16 Q/K/V/W_O to the device, runs `mode`,
  * copies the fp16 [S][d] result back. The copies are inside wall_ms. Buffers should be pinned.
  * Device staging is allocated on the first call for a given shape and reused. In stream mode with a
- * causal mask (and split == 1, NCCL reduction) the work is pipelined over row chunks: rows of chunk c
+ * causal mask (NCCL or NVLS reduction) the work is pipelined over row chunks: rows of chunk c
  * need only the keys of chunks 0..c, so the copy-in of the next chunk, the attention / projection /
  * AllReduce of this one and the copy-out of the previous one overlap. */
 int efa_run_mode_host(efa_ctx* ctx, int mode,
                       const uint16_t* Qh, const uint16_t* Kh, const uint16_t* Vh, const uint16_t* W_O,
                       uint16_t* output, const efa_params* p, efa_run_stats* stats);
+
+/* The same, but only rows [out_row0, out_row0 + out_rows) of the result are copied back, into `output` (which
+ * holds just those rows; NULL or out_rows == 0: nothing is copied back). The reduced result is the same on every
+ * rank, so with several ranks each can bring back its own share of the rows over its own PCIe link
+ * instead of one rank bringing back all of them. Like efa_run_mode_host it has no counterpart in the reference,
+ * whose timed region never leaves the device (run_drivers.cu:218-245). */
+int efa_run_mode_host_rows(efa_ctx* ctx, int mode,
+                           const uint16_t* Qh, const uint16_t* Kh, const uint16_t* Vh, const uint16_t* W_O,
+                           uint16_t* output, int out_row0, int out_rows, const efa_params* p, efa_run_stats* stats);
 
 #ifdef __cplusplus
 }

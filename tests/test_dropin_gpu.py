@@ -18,6 +18,7 @@ pytestmark = pytest.mark.gpu
 EXE = os.path.join(ROOT, "oracle", "_ref", "attn_tests_dropin")
 
 
+@pytest.mark.timeout(700)
 def test_reference_test_program_passes_with_this_librarys_kernels(torch_cuda):
     if not os.path.exists(EXE):
         pytest.skip("oracle/_ref/attn_tests_dropin is not built (needs the reference sources at build time)")
@@ -41,9 +42,7 @@ def test_reference_test_program_passes_with_this_librarys_kernels(torch_cuda):
 EXE_DRIVERS = os.path.join(ROOT, "oracle", "_ref", "attn_tests_dropin_drivers")
 
 
-@pytest.mark.skipif(os.environ.get("EFA_TEST_DROPIN_DRIVERS") != "1",
-                    reason="set EFA_TEST_DROPIN_DRIVERS=1: the run_drivers-level drop-in has run the reference's benchmark "
-                           "program on a B200 but not yet its test program")
+@pytest.mark.timeout(700)
 def test_reference_test_program_passes_with_this_librarys_run_modes(torch_cuda):
     """Both translation units exchanged (make -C oracle dropin_drivers): every tensor-core configuration of the
     reference's run_mode goes through efa_run_mode with fp32 partial sums and output."""
@@ -54,3 +53,11 @@ def test_reference_test_program_passes_with_this_librarys_run_modes(torch_cuda):
     assert r.returncode == 0, tail
     m = re.search(r"(\d+) passed, (\d+) failed, (\d+) skipped", r.stdout)
     assert m and int(m.group(2)) == 0, tail
+    tc_lines, kernel = 0, None
+    for line in r.stdout.splitlines():
+        k = re.match(r"kernel=(\w+) ", line)
+        if k:
+            kernel = k.group(1)
+        elif kernel == "tc" and line.rstrip().endswith("PASS"):
+            tc_lines += 1
+    assert tc_lines == 13 * 3 * 4, tc_lines

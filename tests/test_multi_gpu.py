@@ -147,28 +147,34 @@ def run_workers(tmp_path, nproc, cases, ncomm=3, timeout=1500):
     assert "PASS" in r.stdout
 
 
+@pytest.mark.timeout(1700)
 def test_two_ranks_nccl_reduction(tmp_path):
     run_workers(tmp_path, 2, small(SMALL_2, ("nccl", "nccl_w16", "nccl_f32out")))
 
 
+@pytest.mark.timeout(1700)
 def test_two_ranks_fused_p2p_reduction(tmp_path):
     """stream mode with the projection + reduction fused in one persistent kernel over peer memory."""
     run_workers(tmp_path, 2, small(SMALL_2, ("p2p",)))
 
 
+@pytest.mark.timeout(1700)
 def test_two_ranks_multicast_reduction(tmp_path):
     """every mode with the reduction done by the NVSwitch (multimem.ld_reduce / multimem.st)."""
     run_workers(tmp_path, 2, small(SMALL_2, ("nvls", "nvls_w16"), group_tiles=(0, 1)))
 
 
+@pytest.mark.timeout(1700)
 def test_four_ranks_all_reductions(tmp_path):
     run_workers(tmp_path, 4, small(SMALL_2[:4], ("nccl", "p2p", "nvls"), modes=["megatron", "stream"]))
 
 
+@pytest.mark.timeout(1700)
 def test_eight_ranks_all_reductions(tmp_path):
     run_workers(tmp_path, 8, small(SMALL_8, ("nccl", "nccl_f32out", "p2p", "nvls", "nvls_w16")))
 
 
+@pytest.mark.timeout(2700)
 def test_eight_ranks_benchmark_configurations(tmp_path):
     """The eight-rank configurations of the benchmark plan as whole blocks: S=16384 non-causal and S=32768 causal
     (H=16, d_h=64), S=65536 with 64 / 128 / 256-row tiles, and S=32768, H=32, d_h=128 causal; N(0,1) inputs,
@@ -186,6 +192,7 @@ def test_eight_ranks_benchmark_configurations(tmp_path):
     run_workers(tmp_path, 8, cases, ncomm=4, timeout=2400)
 
 
+@pytest.mark.timeout(2700)
 def test_two_ranks_benchmark_shape(tmp_path):
     """S=32768, H=32, d_h=128 causal on two ranks (16 heads each), all reductions, sampled rows."""
     cases = [dict(shape=[32768, 4096, 32, 128, 2, 1, 1], data="normal", rows=32, reduces=("nccl", "nvls", "p2p"),
