@@ -38,7 +38,7 @@ REDUCE_BY_RANKS = {1: "nccl", 2: "nccl", 4: "nccl", 8: "nccl"}
 
 # DRAM bytes (read + written) of one attention launch of the benchmark shape with all 32 heads on one GPU, by
 # (mode, rows taken last-first): ncu captures, one launch each.
-ATTN_TRAFFIC_32_HEADS = {("stream", False): 5.105e9}
+ATTN_TRAFFIC_32_HEADS = {("stream", False): 5.105e9, ("stream", True): 5.212e9}
 
 
 def measured_peaks():

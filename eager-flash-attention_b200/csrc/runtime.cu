@@ -247,7 +247,10 @@ extern "C" int efa_blocks_per_tile(const efa_params* p)
 extern "C" int efa_stream_plan(const efa_params* p, efa_stream_group* groups, int capacity, int* band_rows, int* descending)
 {
     if (!p || p->tile <= 0 || p->num_tiles <= 0) { set_error("efa_stream_plan: invalid params"); return -1; }
-    const bool desc = p->row_order == EFA_ROWS_DESCENDING || (p->row_order == EFA_ROWS_AUTO && p->causal);
+    // AUTO: last rows first only where nothing has to be hidden behind the attention kernel (one rank): rows then
+    // complete slowly at first and in a rush at the end, which is the wrong way round for a reduction that has to
+    // keep up; with several ranks the first rows go first, as in the reference.
+    const bool desc = p->row_order == EFA_ROWS_DESCENDING || (p->row_order == EFA_ROWS_AUTO && p->causal && p->R == 1);
     if (descending) *descending = desc ? 1 : 0;
     const bool auto_groups = p->group_tiles <= 0;
     int gt = p->group_tiles;
@@ -374,8 +377,8 @@ extern "C" int efa_destroy_ctx(efa_ctx* c)
     for (cudaEvent_t e : c->events) cudaEventDestroy(e);
     for (cudaEvent_t e : c->trace_events) cudaEventDestroy(e);
     for (cudaEvent_t e : {c->ev_t0, c->ev_t1, c->ev_t2, c->ev_t3}) if (e) cudaEventDestroy(e);
-    if (c->counters) cudaFreeHost(c->counters);
-    for (void* q : {c->O_all, c->send_buf, (void*)c->ws_O, (void*)c->ws_m, (void*)c->ws_l,
+    if (c->rescue_stream) cudaStreamDestroy(c->rescue_stream);
+    for (void* q : {c->O_all, c->send_buf, (void*)c->counters, (void*)c->ws_O, (void*)c->ws_m, (void*)c->ws_l,
                     c->h_Q, c->h_K, c->h_V, c->h_W, c->h_out})
         if (q) cudaFree(q);
     delete c;

@@ -24,7 +24,7 @@ struct efa_ctx {
     // Scratch, grown on demand and reused across run_mode calls (freed by efa_destroy_ctx).
     void*  O_all = nullptr;     size_t O_all_bytes = 0;      // fp16 [S][d_local]
     void*  send_buf = nullptr;  size_t send_bytes = 0;       // fp16 [S][d]
-    int*   counters = nullptr;  size_t counters_n = 0;       // mapped pinned host memory: the host can always release a wait
+    int*   counters = nullptr;  size_t counters_n = 0;
     float* ws_O = nullptr; float* ws_m = nullptr; float* ws_l = nullptr;
     size_t ws_O_n = 0, ws_ml_n = 0;
     std::vector<cudaEvent_t> events;                        // disable-timing events, one per tile + a few
@@ -36,6 +36,7 @@ struct efa_ctx {
     size_t h_qkv_bytes = 0, h_w_bytes = 0, h_out_bytes = 0;
 
     cudaStream_t h2d_stream = nullptr, d2h_stream = nullptr;   // copies of the pipelined host-buffer path
+    cudaStream_t rescue_stream = nullptr;                      // carries nothing but the store that releases pending counter waits
 
     P2PState* p2p = nullptr;
     NvlsState* nvls = nullptr;

@@ -165,12 +165,21 @@ struct Run {
     }
 };
 
+// Release every front-end wait on the tile counters by storing a value above any target into them, from a stream
+// that holds nothing else.
+void release_counter_waits(efa_ctx* c, int* counters, size_t ncounters)
+{
+    if (!counters || !ncounters) return;
+    if (!c->rescue_stream && cudaStreamCreateWithFlags(&c->rescue_stream, cudaStreamNonBlocking) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return;
+    }
+    cudaMemsetAsync(counters, 0x7f, ncounters * sizeof(int), c->rescue_stream);
+}
+
 // Wait for a stream with a deadline. When the deadline passes (a tile counter that never reaches its target would
-// block cuStreamWaitValue32 forever), the HOST stores a value above every target into the counters, which live in
-// mapped pinned host memory for exactly this reason: the release must not depend on another stream getting through
-// the GPU's front end, where it can sit in the same hardware queue behind the very wait it is meant to release
-// (measured: a memset from a second stream did not get through). Then the stream is given the same time again to
-// drain, and an error is returned either way.
+// block cuStreamWaitValue32 forever), the counters are overwritten so that every pending wait is released, the
+// stream is given the same time again to drain, and an error is returned either way.
 int sync_stream(efa_ctx* c, cudaStream_t s, int* counters, size_t ncounters)
 {
     const double deadline_ms = c->host_wait_limit_ms;
@@ -193,9 +202,7 @@ int sync_stream(efa_ctx* c, cudaStream_t s, int* counters, size_t ncounters)
     if (first == 2) return 1;
     bool drained = false;
     if (counters && ncounters) {
-        volatile int* host = counters;               // the same words the front end polls (unified addressing)
-        for (size_t i = 0; i < ncounters; i++) host[i] = 0x7f7f7f7f;
-        __sync_synchronize();
+        release_counter_waits(c, counters, ncounters);
         drained = poll(deadline_ms) == 0;
     }
     set_error("stream did not finish within %.1f s; pending tile waits were released%s", deadline_ms / 1e3,
@@ -231,15 +238,10 @@ int scratch(efa_ctx* c, const Run& r, size_t o_rows, size_t send_rows, size_t nc
     if (o_rows && ensure_bytes(&c->O_all, &c->O_all_bytes, o_rows * p.d_local * sizeof(__half))) return 1;
     if (r.nvls()) { if (nvls_prepare(c, p)) return 1; }
     else if (send_rows && ensure_bytes(&c->send_buf, &c->send_bytes, send_rows * r.send_row_bytes())) return 1;
-    if (ncounters > c->counters_n) {
-        // Tile counters: mapped pinned host memory (see sync_stream). The attention kernel adds to them with
-        // fire-and-forget reductions over PCIe, the front end polls them for cuStreamWaitValue32.
-        if (c->counters) { EFA_CUDA(cudaFreeHost(c->counters)); c->counters = nullptr; c->counters_n = 0; }
-        void* hp = nullptr;
-        EFA_CUDA(cudaHostAlloc(&hp, ncounters * sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable));
-        std::memset(hp, 0, ncounters * sizeof(int));
-        c->counters = static_cast<int*>(hp);
-        c->counters_n = ncounters;
+    if (ncounters) {
+        size_t have = c->counters_n * sizeof(int);
+        if (ensure_bytes((void**)&c->counters, &have, ncounters * sizeof(int))) return 1;
+        c->counters_n = have / sizeof(int);
     }
     if (p.split > 1 && ws_rows) {
         size_t haveO = c->ws_O_n * sizeof(float);
@@ -420,9 +422,9 @@ int run_stream(Run& r, char* output, efa_run_stats* st)
     if (world_barrier(c->world)) return 1;
     const double t0 = now_ms();
 
-    // Counters start at zero: a host store (the previous run was waited for on every stream, and the front end reads
-    // these words only after the waits below are enqueued).
-    std::memset(counters, 0, (size_t)p.num_tiles * sizeof(int));
+    cudaEvent_t reset_done = c->events[p.num_tiles];
+    EFA_CUDA(cudaMemsetAsync(counters, 0, (size_t)p.num_tiles * sizeof(int), c->compute_stream));
+    EFA_CUDA(cudaEventRecord(reset_done, c->compute_stream));
     // p.reserve_sms = k runs the attention kernel in its persistent form on (SMs - k) CTAs, so that the
     // projection and the reduction of finished tiles always find an SM. Measured on 8 GPUs (benchmark
     // shape) this loses: the projection of a group is then confined to the k reserved SMs, while with the
@@ -431,6 +433,7 @@ int run_stream(Run& r, char* output, efa_run_stats* st)
     if (r.attention_raw(O_all, p.S, 0, p.S, c->compute_stream, counters, p.tile, p.reserve_sms, band_rows, 0, descending)) return 1;
     EFA_CUDA(cudaEventRecord(c->ev_t1, c->compute_stream));
 
+    EFA_CUDA(cudaStreamWaitEvent(c->proj_stream, reset_done, 0));   // never observe a stale counter
     // Tiles are signalled one by one; the projection and the reduction are launched once per group of
     // consecutive tiles, after a front-end wait on every counter of the group. group_tiles = 1 is the
     // reference's schedule. Small tiles make one launch and one collective per tile cost more than the
@@ -439,10 +442,7 @@ int run_stream(Run& r, char* output, efa_run_stats* st)
     // From here on an error must not leave front-end waits behind on the projection stream: `fail` releases them.
     auto fail = [&]() {
         cudaStreamSynchronize(c->compute_stream);                 // the attention kernel no longer touches the counters
-        volatile int* host = counters;
-        for (int i = 0; i < p.num_tiles; i++) host[i] = 0x7f7f7f7f;
-        __sync_synchronize();
-        cudaStreamSynchronize(c->proj_stream);
+        release_counter_waits(c, counters, (size_t)p.num_tiles);
         return 1;
     };
     for (int gidx = 0; gidx < ngroups; gidx++) {
@@ -466,9 +466,8 @@ int run_stream(Run& r, char* output, efa_run_stats* st)
     const double t_enqueued = now_ms() - t0;
     if (sync_stream(c, c->compute_stream, counters, p.num_tiles) || sync_stream(c, c->proj_stream, counters, p.num_tiles) ||
         sync_comm_streams(c)) {
-        // a wait ran out and the counters were overwritten: let everything that was enqueued drain, then report
-        cudaStreamSynchronize(c->proj_stream);
-        for (int i = 0; i < c->ncomm; i++) cudaStreamSynchronize(c->comm_streams[i]);
+        // a wait ran out and the counters were overwritten: what was enqueued behind the waits now drains (sync_stream
+        // has given it time to); report
         return 1;
     }
     const int rc = finish_timing(c, t0, st, true, false, r.launches);
@@ -532,14 +531,16 @@ int run_stream_host_pipelined(efa_ctx* c, const uint16_t* Qh, const uint16_t* Kh
     auto ev_in = [&](int i) { return c->events[3 * i]; };
     auto ev_proj = [&](int i) { return c->events[3 * i + 1]; };
     auto ev_ar = [&](int i) { return c->events[3 * i + 2]; };
-    cudaEvent_t ev_w = c->events[3 * nchunk];
+    cudaEvent_t ev_w = c->events[3 * nchunk], reset_done = c->events[3 * nchunk + 1];
     const size_t head_pitch = (size_t)p.S * p.d_h * 2;            // bytes between heads, host and device alike
 
     if (world_barrier(c->world)) return 1;
     const double t0 = now_ms();
     EFA_CUDA(cudaMemcpyAsync(dev.W_O, W_O, (size_t)p.d_local * p.d * 2, cudaMemcpyHostToDevice, c->h2d_stream));
     EFA_CUDA(cudaEventRecord(ev_w, c->h2d_stream));
-    std::memset(counters, 0, (size_t)p.num_tiles * sizeof(int));
+    EFA_CUDA(cudaMemsetAsync(counters, 0, (size_t)p.num_tiles * sizeof(int), c->compute_stream));
+    EFA_CUDA(cudaEventRecord(reset_done, c->compute_stream));
+    EFA_CUDA(cudaStreamWaitEvent(c->proj_stream, reset_done, 0));
     EFA_CUDA(cudaStreamWaitEvent(c->proj_stream, ev_w, 0));
     for (int i = 0; i < nchunk; i++) {
         const int t0c = i * ct, nt = (t0c + ct <= p.num_tiles) ? ct : p.num_tiles - t0c;

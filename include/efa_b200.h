@@ -175,7 +175,8 @@ typedef struct efa_params {
     int row_order;              /* stream mode: EFA_ROWS_ASCENDING = tiles complete first to last, the reference's order
                                    (flash_attn_tc.cu:100-103). EFA_ROWS_DESCENDING = last rows first: under a causal mask the
                                    last rows sweep the most keys, so the launch then ends on its shortest work items and
-                                   the consumer waits for the tiles in that same order. AUTO = descending when causal. */
+                                   the consumer waits for the tiles in that same order; but the rows then complete slowly at first and in
+                                   a rush at the end. AUTO = descending for a causal problem on one rank, else ascending. */
     int reduce_ctas;            /* thread blocks of the persistent kernel (P2P), 0 = chosen from the FLOP shares */
     int band_rows;              /* stream mode: rows within which the attention kernel may take its work head by head
                                    instead of in strict row order (K/V reuse in L2); 0 = chosen by efa_stream_plan,

@@ -93,7 +93,7 @@ def test_stream_plan_covers_every_tile_once(pkg):
                         (65536, 256, 7), (1024, 256, 0), (256, 256, 0), (8192, 64, 1000)]:
         for causal, order in [(0, 0), (1, 0), (1, 1), (0, 2)]:
             p, groups, band, desc = _plan(pkg, S, 1024, 16, tile, gt, causal=causal, order=order)
-            assert desc == (order == 2 or (order == 0 and causal == 1))
+            assert desc == (order == 2 or (order == 0 and causal == 1))      # one rank: last rows first when causal
             covered = sorted(t for first, n in groups for t in range(first, first + n))
             assert covered == list(range(p.num_tiles)), (S, tile, gt)
             assert all(n >= 1 for _, n in groups)
@@ -120,9 +120,10 @@ def test_stream_plan_automatic_grouping_tapers_the_eighth_that_completes_last(pk
     p, groups, band, desc = _plan(pkg, 32768, 4096, 32, 128, R=1)
     assert desc and [n for _, n in groups] == [32] * 7 + [16, 8, 8]
     assert groups[0] == (224, 32) and groups[-1] == (0, 8) and groups[-2] == (8, 8)
-    # eight ranks: four heads' K and V (64 MB) stay in the L2, strict row order
+    # eight ranks: four heads' K and V (64 MB) stay in the L2, strict row order; and first rows first, because a
+    # reduction has to keep up with the rows as they complete
     p, groups, band, desc = _plan(pkg, 32768, 4096, 32, 128, R=8)
-    assert band == 0
+    assert band == 0 and not desc and groups[0] == (0, 32)
     # explicit grouping: the band is the group
     p, groups, band, desc = _plan(pkg, 32768, 4096, 32, 128, group_tiles=8)
     assert [n for _, n in groups] == [8] * 32 and band == 1024
