@@ -204,7 +204,7 @@ def main():
     ap.add_argument("--wire", default="auto", choices=["auto", "f16", "f32"],
                     help="element type of the partial sums on the links: the fp32 accumulators (auto), or fp16 (half the bytes, "
                          "one more rounding per partial sum)")
-    ap.add_argument("--order", default="auto", choices=["auto", "asc", "desc"],
+    ap.add_argument("--order", default="auto", choices=["auto", "asc", "desc", "mixed"],
                     help="stream mode: order in which the rows are taken and waited for (auto = last rows first under a causal mask)")
     ap.add_argument("--group-tiles", type=int, default=0, help="tiles per projection + AllReduce launch (0 = auto, 1 = per tile)")
     ap.add_argument("--split", type=int, default=0,
@@ -253,7 +253,7 @@ def main():
     if args.reduce == "auto":
         args.reduce = REDUCE_BY_RANKS.get(world_size, "nccl")
     p.reduce = dict(nccl=pkg.REDUCE_NCCL, p2p=pkg.REDUCE_P2P, nvls=pkg.REDUCE_NVLS)[args.reduce]
-    p.row_order = dict(auto=pkg.ROWS_AUTO, asc=pkg.ROWS_ASCENDING, desc=pkg.ROWS_DESCENDING)[args.order]
+    p.row_order = dict(auto=pkg.ROWS_AUTO, asc=pkg.ROWS_ASCENDING, desc=pkg.ROWS_DESCENDING, mixed=pkg.ROWS_MIXED)[args.order]
     p.wire = dict(auto=pkg.WIRE_AUTO, f16=pkg.WIRE_F16, f32=pkg.WIRE_F32)[args.wire]
     p.group_tiles = args.group_tiles
     mode = pkg.parse_mode(args.mode)

@@ -27,7 +27,7 @@ F32, F16 = 0, 1
 MODE_ATTN, MODE_ATTN_TILED, MODE_MEGATRON, MODE_SYNC, MODE_OVERLAP, MODE_STREAM, MODE_COMM = range(7)
 MODE_NAMES = ("attn", "attn_tiled", "megatron", "sync", "overlap", "stream", "comm")
 REDUCE_NCCL, REDUCE_P2P, REDUCE_NVLS = 0, 1, 2
-ROWS_AUTO, ROWS_ASCENDING, ROWS_DESCENDING = 0, 1, 2
+ROWS_AUTO, ROWS_ASCENDING, ROWS_DESCENDING, ROWS_MIXED = 0, 1, 2, 3
 WIRE_AUTO, WIRE_F16, WIRE_F32 = 0, 1, 2
 RECIPE_REF, RECIPE_NORMAL = 0, 1
 
@@ -109,6 +109,7 @@ _SIGNATURES = {
     "efa_attn_check_params": (C.c_char_p, [C.POINTER(Params)]),
     "efa_blocks_per_tile": (C.c_int, [C.POINTER(Params)]),
     "efa_stream_plan": (C.c_int, [C.POINTER(Params), C.POINTER(StreamGroup), C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "efa_stream_row_blocks": (C.c_int, [C.POINTER(Params), C.POINTER(C.c_short), C.c_int]),
     "efa_ctx_set_wait_limit_ms": (C.c_int, [C.c_void_p, C.c_double, C.c_double]),
     "efa_nvls_output": (C.c_int, [C.c_void_p, C.POINTER(Params), C.POINTER(C.c_void_p)]),
     "efa_world_selftest": (C.c_int, [C.POINTER(WorldStruct)]),
@@ -211,6 +212,17 @@ def stream_plan(p: Params):
     if n < 0:
         raise EfaError(f"stream_plan failed: {last_error()}")
     return [(groups[i].first_tile, groups[i].ntiles) for i in range(n)], band.value, bool(desc.value)
+
+
+def stream_row_blocks(p: Params):
+    """Order of the 256-row blocks of stream mode's attention launch when it is neither first-to-last nor
+    last-to-first (ROWS_MIXED); an empty list otherwise."""
+    cap = (p.S + 255) // 256
+    buf = (C.c_short * max(1, cap))()
+    n = lib().efa_stream_row_blocks(C.byref(p), buf, cap)
+    if n < 0:
+        raise EfaError(f"stream_row_blocks failed: {last_error()}")
+    return [buf[i] for i in range(n)]
 
 
 def mode_name(mode: int) -> str:

@@ -1,6 +1,6 @@
 // attn_bench: benchmark CLI of the tensor-parallel attention block, one process per GPU.
 // Same flags, defaults and CSV columns as attn_bench of eager-flash-attention (attn_bench.cu:48-58,
-// 72-86, 139, 149-152); four columns are appended (tokens_per_s, attn_kernel_ms, reduce, data).
+// 72-86, 139, 149-152); five columns are appended (tokens_per_s, attn_kernel_ms, reduce, data, wire).
 // Ranks come from the MPI subset in mpi_shim/ (start with: efa_launch -n R attn_bench ...).
 //
 //   S,H,d_h,causal,R,kernel,tile,nbuf,split,ncomm,proj,mode,min_ms,max_ms,mean_ms,median_ms,std_ms,...
@@ -96,7 +96,7 @@ static void usage(const char* prog)
         "          [--nbuf 2] [--split 1] [--ncomm 1] [--warmup 3] [--trials 10]\n"
         "          [--modes attn,attn_tiled,megatron,sync,overlap,stream,comm] [--no-header]\n"
         "          [--causal] [--proj fp16|fp32] [--no_prio] [--no_proj] [--no_comm]\n"
-        "          [--reduce nccl|p2p|nvls] [--group_tiles 0] [--order auto|asc|desc] [--data normal|ref] [--seed 42] [--residual]\n"
+        "          [--reduce nccl|p2p|nvls] [--group_tiles 0] [--order auto|asc|desc|mixed] [--data normal|ref] [--seed 42] [--residual]\n"
         "          [--wire auto|f16|f32] [--band_rows 0] [--reserve_sms 0] [--reduce_ctas 0] [--trace] [--own_output]\n", prog);
 }
 
@@ -175,7 +175,8 @@ int main(int argc, char** argv)
     else if (std::strcmp(reduce, "nccl") != 0) fail("--reduce must be nccl, p2p or nvls");
     if (order_s == "asc") p.row_order = EFA_ROWS_ASCENDING;
     else if (order_s == "desc") p.row_order = EFA_ROWS_DESCENDING;
-    else if (order_s != "auto") fail("--order must be auto, asc or desc");
+    else if (order_s == "mixed") p.row_order = EFA_ROWS_MIXED;
+    else if (order_s != "auto") fail("--order must be auto, asc, desc or mixed");
     const std::string wire_s = cl.text("--wire", "auto");
     if (wire_s == "f16") p.wire = EFA_WIRE_F16;
     else if (wire_s == "f32") p.wire = EFA_WIRE_F32;
@@ -223,7 +224,7 @@ int main(int argc, char** argv)
 
     if (g_rank == 0 && header)
         printf("S,H,d_h,causal,R,kernel,tile,nbuf,split,ncomm,proj,mode,min_ms,max_ms,mean_ms,median_ms,std_ms,"
-               "tokens_per_s,attn_kernel_ms,reduce,data\n");
+               "tokens_per_s,attn_kernel_ms,reduce,data,wire\n");
     for (int mode : modes) {
         std::vector<double> times, attn;
         for (int t = 0; t < warmup + trials; t++) {
@@ -242,9 +243,10 @@ int main(int argc, char** argv)
         if (g_rank == 0) {
             const Summary s = summarize(times);
             const Summary a = summarize(attn);
-            printf("%d,%d,%d,%d,%d,%s,%d,%d,%d,%d,%s,%s,%.4f,%.4f,%.4f,%.4f,%.4f,%.1f,%.4f,%s,%s\n",
+            printf("%d,%d,%d,%d,%d,%s,%d,%d,%d,%d,%s,%s,%.4f,%.4f,%.4f,%.4f,%.4f,%.1f,%.4f,%s,%s,%s\n",
                    S, H, d_h, causal, world, kernel, tile, nbuf, split, ncomm, proj, efa_mode_name(mode),
-                   s.lo, s.hi, s.mean, s.median, s.stddev, (double)S / (s.median * 1e-3), a.median, reduce, data);
+                   s.lo, s.hi, s.mean, s.median, s.stddev, (double)S / (s.median * 1e-3), a.median, reduce, data,
+                   p.wire == EFA_WIRE_F16 ? "f16" : "f32");
             fflush(stdout);
         }
     }

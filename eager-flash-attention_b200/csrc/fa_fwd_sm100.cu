@@ -460,7 +460,7 @@ const char* fa_check_params(const efa_flash_params& p, int q_rows)
 int fa_forward(const void* Q, const void* K, const void* V, void* O, int o_dtype,
                const efa_flash_partials* part, int q_start, int q_rows,
                const efa_flash_params& p, cudaStream_t stream, int* tile_counters, int tile_rows, int reserve_sms,
-               int band_rows, int heavy_first)
+               int band_rows, int heavy_first, const short* order_tab)
 {
     if (const char* why = fa_check_params(p, q_rows)) { set_error("flash_attn_tc_forward: %s", why); return 2; }
     if (q_start < 0 || q_start % 64 != 0 || q_start + q_rows > p.S) {
@@ -513,6 +513,7 @@ int fa_forward(const void* Q, const void* K, const void* V, void* O, int o_dtype
     // Nobody waits for particular rows of a launch without counters, so under a causal mask its longest work
     // items (the last rows) go first and the launch ends on short ones; with counters the caller says in which
     // order it will wait for them (first rows first unless told otherwise).
+    a.order_tab = order_tab;
     a.heavy_first = heavy_first >= 0 ? (heavy_first ? 1 : 0) : ((tile_counters == nullptr && p.causal) ? 1 : 0);
 
     const bool f16 = (o_dtype == EFA_F16);
@@ -655,6 +656,7 @@ int fa_forward_noalloc(const void* Q, const void* K, const void* V, void* O, int
     a.counters_sys = 0;
     a.status = status;                       // a word of the module, see noalloc_status()
     a.band_blocks = 0;
+    a.order_tab = nullptr;
     a.heavy_first = 0;
 
     dim3 grid(p.H_local * p.split, (q_rows + FA_BM - 1) / FA_BM);
@@ -680,6 +682,26 @@ int noalloc_status(int* out4, int reset)
         EFA_CUDA(cudaMemcpyToSymbol(g_noalloc_status, zero, sizeof(zero)));
     }
     return 0;
+}
+
+
+namespace {
+template <class K> int touch_kernel(K kernel)
+{
+    cudaFuncAttributes attr;
+    EFA_CUDA(cudaFuncGetAttributes(&attr, kernel));
+    return 0;
+}
+}  // namespace
+
+int fa_preload()
+{
+    return touch_kernel(fa_fwd_kernel<16, true>) || touch_kernel(fa_fwd_kernel<16, false>) ||
+           touch_kernel(fa_fwd_kernel<32, true>) || touch_kernel(fa_fwd_kernel<32, false>) ||
+           touch_kernel(fa_fwd_kernel<64, true>) || touch_kernel(fa_fwd_kernel<64, false>) ||
+           touch_kernel(fa_fwd_kernel<128, true>) || touch_kernel(fa_fwd_kernel<128, false>) ||
+           touch_kernel(combine_splits_kernel<true>) || touch_kernel(combine_splits_kernel<false>) ||
+           touch_kernel(f32_to_f16_kernel) || fa_ws_preload();
 }
 
 }  // namespace efa

@@ -15,8 +15,9 @@ int fa_forward(const void* Q, const void* K, const void* V, void* O, int o_dtype
                int band_rows = 0,      // d_h 64/128 with counters: rows may complete in bands of this many rows
                                        // (better K/V reuse in L2); 0 = strict row order. Without counters the
                                        // order is free and whole heads are processed one after another.
-               int heavy_first = -1);  // d_h 64/128: 1 = take the row blocks (or bands) from the last to the first, 0 = from
+               int heavy_first = -1,  // d_h 64/128: 1 = take the row blocks (or bands) from the last to the first, 0 = from
                                        // the first; -1 = last first exactly when there are no counters and the mask is causal
+               const short* order_tab = nullptr);  // d_h 64/128, band_rows == 0: the order of the 256-row blocks (device memory)
 
 // Split-KV attention + merge with the partials in a fixed device array (no allocation anywhere).
 int fa_forward_noalloc(const void* Q, const void* K, const void* V, void* O, int o_dtype,

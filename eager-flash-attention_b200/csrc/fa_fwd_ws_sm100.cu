@@ -201,7 +201,8 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmQ,
             item_y = b * band + rem % nb;
             // Longest items first: list scheduling then ends on the shortest items instead of the longest, which
             // is worth up to one item's duration (a fifth of the launch with four heads per GPU at 32k rows).
-            if (a.heavy_first) item_y = items_y - 1 - item_y;
+            if (a.order_tab != nullptr && band == 1) item_y = a.order_tab[item_y];
+            else if (a.heavy_first) item_y = items_y - 1 - item_y;
         }
         it.head  = item_x % a.H_local;
         it.split = item_x / a.H_local;
@@ -597,5 +598,25 @@ int fa_forward_ws(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMa
 }
 
 int fa_ws_kv_box_rows() { return WS_BN; }
+
+
+namespace {
+template <class K> int touch_kernel(K kernel)
+{
+    cudaFuncAttributes attr;
+    EFA_CUDA(cudaFuncGetAttributes(&attr, kernel));
+    return 0;
+}
+}  // namespace
+
+// Loads the code of every instantiation now. A kernel's first launch may otherwise have to wait for the device to go
+// idle, which it never does while a stream sits in a front-end wait on a counter that is not coming.
+int fa_ws_preload()
+{
+    return touch_kernel(fa_fwd_ws_kernel<64, true, false>) || touch_kernel(fa_fwd_ws_kernel<64, false, false>) ||
+           touch_kernel(fa_fwd_ws_kernel<64, true, true>) || touch_kernel(fa_fwd_ws_kernel<64, false, true>) ||
+           touch_kernel(fa_fwd_ws_kernel<128, true, false>) || touch_kernel(fa_fwd_ws_kernel<128, false, false>) ||
+           touch_kernel(fa_fwd_ws_kernel<128, true, true>) || touch_kernel(fa_fwd_ws_kernel<128, false, true>);
+}
 
 }  // namespace efa

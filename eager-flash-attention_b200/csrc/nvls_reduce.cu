@@ -437,4 +437,16 @@ void nvls_destroy(efa_ctx* c)
     c->nvls = nullptr;
 }
 
+
+namespace {
+template <class K> int touch_kernel(K kernel)
+{
+    cudaFuncAttributes attr;
+    EFA_CUDA(cudaFuncGetAttributes(&attr, kernel));
+    return 0;
+}
+}  // namespace
+
+int nvls_preload() { return touch_kernel(nvls_allreduce_kernel<true>) || touch_kernel(nvls_allreduce_kernel<false>); }
+
 }  // namespace efa

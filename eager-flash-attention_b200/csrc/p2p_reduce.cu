@@ -626,4 +626,16 @@ void p2p_destroy(efa_ctx* c)
     c->p2p = nullptr;
 }
 
+
+namespace {
+template <class K> int touch_kernel(K kernel)
+{
+    cudaFuncAttributes attr;
+    EFA_CUDA(cudaFuncGetAttributes(&attr, kernel));
+    return 0;
+}
+}  // namespace
+
+int p2p_preload() { return touch_kernel(tile_proj_reduce_kernel<128>) || touch_kernel(tile_proj_reduce_kernel<256>); }
+
 }  // namespace efa

@@ -208,4 +208,20 @@ int project_f16(const void* A, const void* W, void* out, int rows, int d_local, 
     return wide ? launch_proj<256, false>(ta, tw, a, stream) : launch_proj<128, false>(ta, tw, a, stream);
 }
 
+
+namespace {
+template <class K> int touch_kernel(K kernel)
+{
+    cudaFuncAttributes attr;
+    EFA_CUDA(cudaFuncGetAttributes(&attr, kernel));
+    return 0;
+}
+}  // namespace
+
+int proj_preload()
+{
+    return touch_kernel(proj_gemm_kernel<128, false>) || touch_kernel(proj_gemm_kernel<128, true>) ||
+           touch_kernel(proj_gemm_kernel<256, false>) || touch_kernel(proj_gemm_kernel<256, true>);
+}
+
 }  // namespace efa

@@ -18,6 +18,9 @@
 
 namespace efa {
 
+// Load the code of every kernel of the library on the current device (one function per translation unit).
+int fa_preload(); int proj_preload(); int p2p_preload(); int nvls_preload(); int modes_preload();
+
 int world_barrier(const efa_world& w)
 {
     if (w.size <= 1 || !w.barrier) return 0;
@@ -244,24 +247,63 @@ extern "C" int efa_blocks_per_tile(const efa_params* p)
     return (p->tile / 64) * p->H_local * p->split;
 }
 
+namespace {
+
+// EFA_ROWS_MIXED applies to a causal problem in strict row order (no bands): otherwise it is first-to-last.
+bool mixed_order(const efa_params* p)
+{
+    if (p->row_order != EFA_ROWS_MIXED || !p->causal || p->band_rows > 0) return false;
+    const double kv_bytes = 2.0 * (double)p->H_local * p->S * p->d_h * 2.0;
+    return kv_bytes <= 80e6 || p->band_rows < 0;
+}
+
+// Two 256-row blocks from the end, one from the start, and so on.
+int mixed_blocks(const efa_params* p, std::vector<short>& order)
+{
+    const int nb = (p->S + 255) / 256;
+    order.clear();
+    int lo = 0, hi = nb - 1;
+    while (lo <= hi) {
+        for (int k = 0; k < 2 && hi >= lo; k++) order.push_back((short)hi--);
+        if (lo <= hi) order.push_back((short)lo++);
+    }
+    return nb;
+}
+
+}  // namespace
+
+extern "C" int efa_stream_row_blocks(const efa_params* p, short* blocks, int capacity)
+{
+    if (!p || p->S <= 0) { set_error("efa_stream_row_blocks: invalid params"); return -1; }
+    if (!mixed_order(p)) return 0;
+    std::vector<short> order;
+    const int nb = mixed_blocks(p, order);
+    if (nb > 32767) { set_error("efa_stream_row_blocks: too many row blocks"); return -1; }
+    if (blocks) {
+        if (capacity < nb) { set_error("efa_stream_row_blocks: %d blocks, room for %d", nb, capacity); return -1; }
+        std::copy(order.begin(), order.end(), blocks);
+    }
+    return nb;
+}
+
 extern "C" int efa_stream_plan(const efa_params* p, efa_stream_group* groups, int capacity, int* band_rows, int* descending)
 {
     if (!p || p->tile <= 0 || p->num_tiles <= 0) { set_error("efa_stream_plan: invalid params"); return -1; }
+    const bool mixed = mixed_order(p);
     // AUTO: last rows first only where nothing has to be hidden behind the attention kernel (one rank): rows then
     // complete slowly at first and in a rush at the end, which is the wrong way round for a reduction that has to
     // keep up; with several ranks the first rows go first, as in the reference.
-    const bool desc = p->row_order == EFA_ROWS_DESCENDING || (p->row_order == EFA_ROWS_AUTO && p->causal && p->R == 1);
+    const bool desc = !mixed && (p->row_order == EFA_ROWS_DESCENDING || (p->row_order == EFA_ROWS_AUTO && p->causal && p->R == 1));
     if (descending) *descending = desc ? 1 : 0;
     const bool auto_groups = p->group_tiles <= 0;
     int gt = p->group_tiles;
-    if (auto_groups) { gt = (p->S / 8) / p->tile; if (gt < 1) gt = 1; }
+    if (auto_groups) { gt = (p->S / (mixed ? 16 : 8)) / p->tile; if (gt < 1) gt = 1; }
     if (gt > p->num_tiles) gt = p->num_tiles;
     int n = 0, smallest = p->num_tiles;
-    // Laid out in time order over positions 0 .. num_tiles: position x is tile x (ascending) or tile
-    // num_tiles - 1 - x (descending).
+    // Laid out over positions 0 .. num_tiles: position x is tile x, or tile num_tiles - 1 - x (descending).
     for (int t0 = 0; t0 < p->num_tiles; n++) {
         int nt = (t0 + gt <= p->num_tiles) ? gt : p->num_tiles - t0;
-        if (auto_groups && gt >= 4 && t0 + gt >= p->num_tiles) {
+        if (auto_groups && !mixed && gt >= 4 && t0 + gt >= p->num_tiles) {
             // the eighth that completes last: S/16, S/32, S/32 rows
             const int left = p->num_tiles - t0;
             nt = (left > gt / 2) ? gt / 2 : (left > gt / 4 ? left - gt / 4 : left);
@@ -274,6 +316,33 @@ extern "C" int efa_stream_plan(const efa_params* p, efa_stream_group* groups, in
         }
         if (nt < smallest) smallest = nt;
         t0 += nt;
+    }
+    if (mixed && groups) {
+        // Order the groups as a list schedule of the work items completes them: items (one per 256-row block, head
+        // and split) go to the SM that is free first, in dispatch order, and cost their number of key stages.
+        std::vector<short> order;
+        const int nb = mixed_blocks(p, order);
+        const int per_block = p->H_local * p->split, sms = 148;
+        std::vector<double> free_at(sms, 0.0), done(nb, 0.0);
+        for (int k = 0; k < nb; k++) {
+            const int y = order[k];
+            for (int i = 0; i < per_block; i++) {
+                auto it = std::min_element(free_at.begin(), free_at.end());
+                *it += 2.0 * (y + 1) / p->split + 3.0;
+                done[y] = std::max(done[y], *it);
+            }
+        }
+        std::vector<std::pair<double, int>> key(n);
+        for (int g = 0; g < n; g++) {
+            const int r0 = groups[g].first_tile * p->tile, r1 = (groups[g].first_tile + groups[g].ntiles) * p->tile;
+            double t = 0.0;
+            for (int y = r0 / 256; y <= (r1 - 1) / 256 && y < nb; y++) t = std::max(t, done[y]);
+            key[g] = {t, g};
+        }
+        std::sort(key.begin(), key.end());
+        std::vector<efa_stream_group> sorted(n);
+        for (int g = 0; g < n; g++) sorted[g] = groups[key[g].second];
+        std::copy(sorted.begin(), sorted.end(), groups);
     }
     if (band_rows) {
         // Rows only have to complete group by group, so the attention kernel may order its work in bands no longer
@@ -288,7 +357,7 @@ extern "C" int efa_stream_plan(const efa_params* p, efa_stream_group* groups, in
         const double kv_bytes = 2.0 * (double)p->H_local * p->S * p->d_h * 2.0;
         if (kv_bytes <= 80e6) b = 0;
         if (p->band_rows > 0) b = (p->band_rows / 256) * 256;
-        if (p->band_rows < 0) b = 0;
+        if (p->band_rows < 0 || mixed) b = 0;
         *band_rows = b;
     }
     return n;
@@ -334,6 +403,21 @@ extern "C" int efa_make_ctx(efa_ctx** out, const efa_world* world, int ncomm, in
         ncclResult_t r = nccl->CommInitRank(&c->nccls[i], world->size, id, world->rank);
         if (r != ncclSuccess) { set_error("ncclCommInitRank: %s", nccl->GetErrorString(r)); return 1; }
     }
+    // Everything a run enqueues behind a front-end wait must be loaded before the first wait exists: a first launch
+    // that has to load code may wait for the device to go idle, and a stream that waits for a counter that is not
+    // coming never is. So: every kernel of this library, and NCCL's (one eight-byte AllReduce per communicator).
+    if (fa_preload() || proj_preload() || p2p_preload() || nvls_preload() || modes_preload()) return 1;
+    {
+        float* warm = nullptr;
+        EFA_CUDA(cudaMalloc(&warm, 2 * sizeof(float)));
+        EFA_CUDA(cudaMemset(warm, 0, 2 * sizeof(float)));
+        for (int i = 0; i < ncomm; i++) {
+            ncclResult_t r = nccl->AllReduce(warm, warm, 2, ncclFloat, ncclSum, c->nccls[i], c->comm_streams[i]);
+            if (r != ncclSuccess) { set_error("ncclAllReduce (warm-up): %s", nccl->GetErrorString(r)); return 1; }
+            EFA_CUDA(cudaStreamSynchronize(c->comm_streams[i]));
+        }
+        EFA_CUDA(cudaFree(warm));
+    }
     EFA_CUDA(cudaEventCreate(&c->ev_t0));
     EFA_CUDA(cudaEventCreate(&c->ev_t1));
     EFA_CUDA(cudaEventCreate(&c->ev_t2));
@@ -378,7 +462,7 @@ extern "C" int efa_destroy_ctx(efa_ctx* c)
     for (cudaEvent_t e : c->trace_events) cudaEventDestroy(e);
     for (cudaEvent_t e : {c->ev_t0, c->ev_t1, c->ev_t2, c->ev_t3}) if (e) cudaEventDestroy(e);
     if (c->rescue_stream) cudaStreamDestroy(c->rescue_stream);
-    for (void* q : {c->O_all, c->send_buf, (void*)c->counters, (void*)c->ws_O, (void*)c->ws_m, (void*)c->ws_l,
+    for (void* q : {c->O_all, c->send_buf, (void*)c->counters, (void*)c->order_tab, (void*)c->ws_O, (void*)c->ws_m, (void*)c->ws_l,
                     c->h_Q, c->h_K, c->h_V, c->h_W, c->h_out})
         if (q) cudaFree(q);
     delete c;

@@ -38,6 +38,9 @@ struct efa_ctx {
     cudaStream_t h2d_stream = nullptr, d2h_stream = nullptr;   // copies of the pipelined host-buffer path
     cudaStream_t rescue_stream = nullptr;                      // carries nothing but the store that releases pending counter waits
 
+    short* order_tab = nullptr; size_t order_tab_n = 0;        // device copy of the row-block order of the last mixed-order run
+    std::vector<short> order_tab_host;
+
     P2PState* p2p = nullptr;
     NvlsState* nvls = nullptr;
     int nvls_ctas = 16;                                        // thread blocks of one multicast reduction (fixed per context)

@@ -97,7 +97,7 @@ struct Run {
     // ws_row0: workspace row that the launch's first row maps to (split partials of several launches side by side).
     // heavy_first: -1 = the kernel's default (last rows first when nobody waits for counters), 0 / 1 = first / last rows first.
     int attention_raw(__half* O, int ws_rows, int q_start, int q_rows, cudaStream_t s, int* counters, int tile_rows,
-                      int reserve_sms = 0, int band_rows = 0, int ws_row0 = 0, int heavy_first = -1)
+                      int reserve_sms = 0, int band_rows = 0, int ws_row0 = 0, int heavy_first = -1, const short* order_tab = nullptr)
     {
         efa_flash_partials q = ws(ws_rows);
         if (q.O_part && ws_row0 > 0) {
@@ -107,7 +107,7 @@ struct Run {
         }
         launches++;
         return fa_forward(w.Qh, w.Kh, w.Vh, O, EFA_F16, &q, q_start, q_rows, p.flash_tc, s, counters, tile_rows, reserve_sms,
-                          band_rows, heavy_first);
+                          band_rows, heavy_first, order_tab);
     }
     // launch_combine (attn_main.cu:247-252): no-op when split == 1.
     int combine(__half* O, int ws_rows, int row0, int rows, cudaStream_t s)
@@ -429,8 +429,27 @@ int run_stream(Run& r, char* output, efa_run_stats* st)
     // projection and the reduction of finished tiles always find an SM. Measured on 8 GPUs (benchmark
     // shape) this loses: the projection of a group is then confined to the k reserved SMs, while with the
     // plain grid its CTAs (higher stream priority) spread over every SM an attention CTA retires from.
+    // EFA_ROWS_MIXED: the order of the 256-row blocks as a table in device memory (uploaded when it changes)
+    const short* order_tab = nullptr;
+    {
+        std::vector<short> order(((size_t)p.S + 255) / 256);
+        const int nb = efa_stream_row_blocks(&p, order.data(), (int)order.size());
+        if (nb < 0) return 1;
+        if (nb > 0) {
+            order.resize(nb);
+            if (order != c->order_tab_host) {
+                size_t have = c->order_tab_n * sizeof(short);
+                if (ensure_bytes((void**)&c->order_tab, &have, order.size() * sizeof(short))) return 1;
+                c->order_tab_n = have / sizeof(short);
+                c->order_tab_host = order;
+                EFA_CUDA(cudaMemcpyAsync(c->order_tab, c->order_tab_host.data(), order.size() * sizeof(short),
+                                         cudaMemcpyHostToDevice, c->compute_stream));
+            }
+            order_tab = c->order_tab;
+        }
+    }
     EFA_CUDA(cudaEventRecord(c->ev_t0, c->compute_stream));
-    if (r.attention_raw(O_all, p.S, 0, p.S, c->compute_stream, counters, p.tile, p.reserve_sms, band_rows, 0, descending)) return 1;
+    if (r.attention_raw(O_all, p.S, 0, p.S, c->compute_stream, counters, p.tile, p.reserve_sms, band_rows, 0, descending, order_tab)) return 1;
     EFA_CUDA(cudaEventRecord(c->ev_t1, c->compute_stream));
 
     EFA_CUDA(cudaStreamWaitEvent(c->proj_stream, reset_done, 0));   // never observe a stale counter
@@ -516,9 +535,22 @@ int run_stream_host_pipelined(efa_ctx* c, const uint16_t* Qh, const uint16_t* Kh
     // Chunks of about S/8 rows, whole tiles, and every chunk boundary a multiple of 128 rows: the attention
     // kernels load keys in stages of up to 128 rows, and a stage must never reach into rows of the next chunk,
     // which are still on their way to the device.
+    // The copy-in is the long pole (three tensors over PCIe), so what follows the last copy-in should be short: the
+    // last eighth of the rows is cut into S/16, S/32 and S/32 where the alignment allows.
     int ct = (p.S / 8) / p.tile; if (ct < 1) ct = 1;
     while (((long)ct * p.tile) % 128 != 0) ct++;
-    const int nchunk = (p.num_tiles + ct - 1) / ct;
+    std::vector<int> chunk_first, chunk_tiles;          // in tiles
+    for (int t = 0; t < p.num_tiles; ) {
+        int nt = std::min(ct, p.num_tiles - t);
+        if (t + ct >= p.num_tiles && nt == ct && ct % 4 == 0 && ((long)(ct / 4) * p.tile) % 128 == 0) {
+            const int parts[3] = {ct / 2, ct / 4, ct / 4};
+            for (int k = 0; k < 3; k++) { chunk_first.push_back(t); chunk_tiles.push_back(parts[k]); t += parts[k]; }
+            break;
+        }
+        chunk_first.push_back(t); chunk_tiles.push_back(nt);
+        t += nt;
+    }
+    const int nchunk = (int)chunk_first.size();
     Run r{c, dev, p};
     if (scratch(c, r, p.S, p.S, p.num_tiles, p.S, (size_t)3 * nchunk + 2)) return 1;
     __half* O_all = static_cast<__half*>(c->O_all);
@@ -543,7 +575,7 @@ int run_stream_host_pipelined(efa_ctx* c, const uint16_t* Qh, const uint16_t* Kh
     EFA_CUDA(cudaStreamWaitEvent(c->proj_stream, reset_done, 0));
     EFA_CUDA(cudaStreamWaitEvent(c->proj_stream, ev_w, 0));
     for (int i = 0; i < nchunk; i++) {
-        const int t0c = i * ct, nt = (t0c + ct <= p.num_tiles) ? ct : p.num_tiles - t0c;
+        const int t0c = chunk_first[i], nt = chunk_tiles[i];
         const int row0 = t0c * p.tile, rows = nt * p.tile;
         const size_t off = (size_t)row0 * p.d_h * 2, width = (size_t)rows * p.d_h * 2;
         // rows [row0, row0 + rows) of every head: one strided copy per tensor
@@ -585,6 +617,13 @@ int run_stream_host_pipelined(efa_ctx* c, const uint16_t* Qh, const uint16_t* Kh
     if (sync_comm_streams(c)) return 1;
     if (sync_stream(c, c->d2h_stream, nullptr, 0)) return 1;
     return finish_timing(c, t0, stats, false, false, r.launches);
+}
+
+int modes_preload()
+{
+    cudaFuncAttributes attr;
+    EFA_CUDA(cudaFuncGetAttributes(&attr, add_residual_kernel));
+    return 0;
 }
 
 int run_mode_impl(efa_ctx* c, int mode, const efa_weights& w, void* output, const efa_params& p, efa_run_stats* stats,

@@ -21,7 +21,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 PKG = os.path.dirname(HERE)
 HEADER = ("S,H,d_h,causal,R,kernel,tile,nbuf,split,ncomm,proj,mode,min_ms,max_ms,mean_ms,median_ms,std_ms,"
-          "tokens_per_s,attn_kernel_ms,reduce,data")
+          "tokens_per_s,attn_kernel_ms,reduce,data,wire")
 
 
 def suite_commands(name, ranks):

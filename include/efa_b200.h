@@ -153,7 +153,7 @@ enum { EFA_REDUCE_NCCL = 0, EFA_REDUCE_P2P = 1, EFA_REDUCE_NVLS = 2 };
 enum { EFA_WIRE_AUTO = 0, EFA_WIRE_F16 = 1, EFA_WIRE_F32 = 2 };
 
 /* Order in which stream mode takes the rows of a causal problem (row_order). */
-enum { EFA_ROWS_AUTO = 0, EFA_ROWS_ASCENDING = 1, EFA_ROWS_DESCENDING = 2 };
+enum { EFA_ROWS_AUTO = 0, EFA_ROWS_ASCENDING = 1, EFA_ROWS_DESCENDING = 2, EFA_ROWS_MIXED = 3 };
 
 /* Derived problem description: AttnParams (attn_defs.cuh:70-84) without the fields of the
  * removed legacy kernel (B_M, B_N, kernel, flash). */
@@ -176,7 +176,10 @@ typedef struct efa_params {
                                    (flash_attn_tc.cu:100-103). EFA_ROWS_DESCENDING = last rows first: under a causal mask the
                                    last rows sweep the most keys, so the launch then ends on its shortest work items and
                                    the consumer waits for the tiles in that same order; but the rows then complete slowly at first and in
-                                   a rush at the end. AUTO = descending for a causal problem on one rank, else ascending. */
+                                   a rush at the end. EFA_ROWS_MIXED (causal, strict row order) = two blocks from the end, one
+                                   from the start, and so on: rows complete at a steady rate from both ends and the launch
+                                   still ends on middle-weight items. AUTO = descending for a causal problem on one rank,
+                                   else ascending. */
     int reduce_ctas;            /* thread blocks of the persistent kernel (P2P), 0 = chosen from the FLOP shares */
     int band_rows;              /* stream mode: rows within which the attention kernel may take its work head by head
                                    instead of in strict row order (K/V reuse in L2); 0 = chosen by efa_stream_plan,
@@ -207,7 +210,8 @@ int efa_blocks_per_tile(const efa_params* p);
 /* The launch plan of stream mode (the loop of run_stream, run_drivers.cu:227-240, which there is one tile per
  * iteration): consecutive tiles [first_tile, first_tile + ntiles) share one projection launch and one reduction
  * after a cuStreamWaitValue32 on each of their counters. Groups are returned in the order in which they are
- * waited for: first to last rows, or (*descending = 1) last to first.
+ * waited for: first to last rows, (*descending = 1) last to first, or for EFA_ROWS_MIXED (S/16 rows per group) in the
+ * order in which a list schedule of the work items on the device's SMs completes them.
  * group_tiles > 0: groups of that many tiles (1 = the reference's schedule). group_tiles == 0: about S/8
  * rows per group and the eighth that completes last cut into S/16, S/32, S/32, so that what remains after the
  * attention kernel ends is small. *band_rows (if not NULL): the band within which the attention kernel may take
@@ -216,6 +220,10 @@ int efa_blocks_per_tile(const efa_params* p);
  * Returns the number of groups (groups may be NULL to count them), -1 on error. */
 typedef struct efa_stream_group { int first_tile, ntiles; } efa_stream_group;
 int efa_stream_plan(const efa_params* p, efa_stream_group* groups, int capacity, int* band_rows, int* descending);
+/* The order in which stream mode's attention launch takes its 256-row blocks when it is neither first-to-last nor
+ * last-to-first (EFA_ROWS_MIXED): blocks[k] = index of the block taken k-th. Returns the number of blocks, 0 when the
+ * order of `p` is one of the two plain ones, -1 on error. Host arithmetic only. */
+int efa_stream_row_blocks(const efa_params* p, short* blocks, int capacity);
 
 /* Host control plane of one rank. The reference uses MPI for exactly these four operations
  * (MPI_Barrier / MPI_Allreduce(MAX) / MPI_Bcast / and, new here, an all-gather of opaque bytes for

@@ -137,6 +137,26 @@ def test_stream_plan_automatic_grouping_tapers_the_eighth_that_completes_last(pk
     assert [n for _, n in groups] == [1, 1, 1, 1] and band == 0
 
 
+def test_stream_plan_mixed_order(pkg):
+    # two 256-row blocks from the end, one from the start; groups of S/16 rows in the order a list schedule completes them
+    p = pkg.make_params(32768, 4096, 32, 128, causal=1, world_size=8)
+    p.row_order = pkg.ROWS_MIXED
+    order = pkg.stream_row_blocks(p)
+    assert sorted(order) == list(range(128)) and order[:6] == [127, 126, 0, 125, 124, 1]
+    groups, band, desc = pkg.stream_plan(p)
+    assert band == 0 and not desc
+    assert sorted(groups) == [(16 * g, 16) for g in range(16)]
+    assert groups[0] == (0, 16)                         # the lightest rows complete first ...
+    assert groups[-1][0] not in (0, 240)                # ... and neither end completes last
+    # not causal, or bands in use (K and V of the local heads exceed the L2): plain first-to-last order
+    q = pkg.make_params(32768, 4096, 32, 128, causal=0, world_size=8)
+    q.row_order = pkg.ROWS_MIXED
+    assert pkg.stream_row_blocks(q) == [] and pkg.stream_plan(q)[0][0] == (0, 32)
+    q = pkg.make_params(32768, 4096, 32, 128, causal=1, world_size=1)
+    q.row_order = pkg.ROWS_MIXED
+    assert pkg.stream_row_blocks(q) == [] and pkg.stream_plan(q)[1] == 2048
+
+
 def test_stream_plan_counts_without_a_buffer_and_rejects_a_short_one(pkg):
     import ctypes as C
     p = pkg.make_params(32768, 4096, 32, 128, causal=1, world_size=1)

@@ -142,6 +142,33 @@ def test_stream_mode_with_the_fused_projection_kernel_single_rank(pkg, oracle, t
         assert_close(oracle, got if rows is None else got[rows], ref, f"rep {rep}")
 
 
+@pytest.mark.parametrize("order", ["ASCENDING", "DESCENDING", "MIXED"])
+@pytest.mark.parametrize("case", [(4096, 1024, 16, 128, 1), (2048, 1024, 8, 64, 2), (1280, 512, 8, 128, 1)],
+                         ids=lambda c: "S%d_d%d_H%d_t%d_s%d" % c)
+def test_stream_mode_row_orders(pkg, oracle, torch_cuda, ctx, case, order):
+    """Causal stream mode with the rows taken first-to-last, last-to-first and mixed (two blocks from the end, one from
+    the start): the consumer waits for the groups in the order the attention launch completes them."""
+    torch = torch_cuda
+    S, d, H, tile, split = case
+    p = pkg.make_params(S, d, H, tile, 2, split, 1)
+    p.row_order = getattr(pkg, "ROWS_" + order)
+    if order == "MIXED":
+        assert sorted(pkg.stream_row_blocks(p)) == list(range((S + 255) // 256))
+    bits, vals = ref_inputs_f16(oracle, S, d, H, 1, 0, 42) if S <= 2048 else normal_inputs_f16(pkg, oracle, p, 0, 42)
+    rows = None if S <= 2048 else np.arange(0, S, 13, dtype=np.int32)
+    ref = oracle.block_rows([vals], d, 1, rows)
+    dev = to_dev(torch, bits)
+    w = pkg.Weights(*(t.data_ptr() for t in dev))
+    for rep in range(2):
+        out = torch.full((S, d), float("nan"), dtype=torch.float16, device="cuda")
+        pkg.kernel_status_reset()
+        pkg.run_mode(ctx, pkg.MODE_STREAM, w, out, p)
+        torch.cuda.synchronize()
+        assert pkg.kernel_status()[0] == 0, pkg.kernel_status()
+        got = out.float().cpu().numpy()
+        assert_close(oracle, got if rows is None else got[rows], ref, f"{order} rep {rep}")
+
+
 @pytest.mark.parametrize("case", [(1024, 512, 8, 128, 1, 1), (2048, 1024, 8, 256, 0, 1), (4096, 1024, 16, 128, 1, 1), (2048, 512, 8, 128, 1, 2)],
                          ids=lambda c: "S%d_d%d_H%d_t%d_c%d_s%d" % c)
 def test_stream_mode_with_reserved_sms(pkg, oracle, torch_cuda, ctx, case):
