@@ -29,6 +29,7 @@
 
 #include <cstddef>
 #include <cstring>
+#include <vector>
 
 struct NvlsState {
     int R = 0, rank = 0;
@@ -39,15 +40,25 @@ struct NvlsState {
     CUdevice dev = 0;
     bool have_mem = false, have_mc = false, bound = false, uc_mapped = false, mc_mapped = false;
     unsigned seq[EFA_MAX_COMM] = {}; // barriers done per slot (same on all ranks)
+    // EFA_REDUCE_PULL: fp32 partial sums in plain device memory that every rank maps (CUDA IPC)
+    float* pull_send = nullptr;
+    size_t pull_bytes = 0;
+    float* pull_peer[8] = {};
+    void*  pull_opened[8] = {};      // what cudaIpcOpenMemHandle returned, per peer
+    int    pull_ctas = 0;            // grid of the pulling kernel, fixed while these buffers live (it has flags and counts of its own)
+    unsigned pull_seq[EFA_MAX_COMM] = {};
 };
 
 namespace efa {
 
 namespace {
 
-constexpr int    NV_THREADS   = 512;
+#ifndef EFA_NV_THREADS
+#define EFA_NV_THREADS 512
+#endif
+constexpr int    NV_THREADS   = EFA_NV_THREADS;
 constexpr int    NV_MAX_CTAS  = 64;
-constexpr size_t NV_FLAG_BYTES = 64 * 1024;             // EFA_MAX_COMM slots x NV_MAX_CTAS flags, padded
+constexpr size_t NV_FLAG_BYTES = 64 * 1024;             // two banks (in-switch, pulling) of EFA_MAX_COMM slots x NV_MAX_CTAS flags, padded
 
 struct NvArgs {
     const char* mc_send;       // multicast view of the partial sums
@@ -92,66 +103,213 @@ __device__ __forceinline__ void multimem_st(char* mc_addr, const uint4& v)
 }
 
 // Thread 0 of the block: add 1 to this block's flag on every rank, then wait until all ranks did.
-__device__ __forceinline__ bool block_barrier(const NvArgs& a, unsigned target, int site, int* abort_word)
+__device__ __forceinline__ bool block_barrier(unsigned* flags_mc, const unsigned* flags_uc, unsigned long long limit_ns,
+                                              unsigned target, int site, int* abort_word)
 {
     __threadfence_system();
-    multimem_red_add(a.flags_mc + blockIdx.x, 1u);
+    multimem_red_add(flags_mc + blockIdx.x, 1u);
     const unsigned long long t0 = globaltimer_ns();
     int spins = 0;
     while (true) {
-        const unsigned v = ld_acquire_sys_u32(a.flags_uc + blockIdx.x);
+        const unsigned v = ld_acquire_sys_u32(flags_uc + blockIdx.x);
         if ((int)(v - target) >= 0) return true;
-        if ((++spins & 15) == 0 && globaltimer_ns() - t0 > a.limit_ns) { *abort_word = site; return false; }
+        if ((++spins & 15) == 0 && globaltimer_ns() - t0 > limit_ns) { *abort_word = site; return false; }
         __nanosleep(spins < 64 ? 50 : 400);
     }
 }
 
-// WIRE_F32: the partial sums are fp32 (two 16-byte loads per 8 elements, summed in fp32 by the switch, rounded here,
-// once); otherwise fp16 (one load per 8 elements, fp32 accumulation and the rounding inside the switch).
+// The data loop. A warp works on runs of 256 elements: 512 bytes of fp16 results, one 16-byte store per lane.
+//   fp16 partial sums: one 16-byte load per lane (fp32 accumulation and the rounding inside the switch).
+//   WIRE_F32: the partial sums are fp32, 1 KB per run. Lane l loads bytes [16 l, 16 l + 16) and [512 + 16 l, ...):
+//   every load instruction of the warp covers 512 contiguous bytes. The switch sums in fp32, the lane rounds
+//   (once), and neighbouring lanes swap halves so that each again owns 16 contiguous bytes of the result: an
+//   even lane l stores elements [4 l, 4 l + 8) of the run, an odd lane [128 + 4 (l - 1), ... + 8).
+// LOADS 16-byte loads are in flight per thread before the first store.
+#ifndef EFA_NV_LOADS
+#define EFA_NV_LOADS 8
+#endif
 template <bool WIRE_F32>
 __global__ void __launch_bounds__(NV_THREADS)
 nvls_allreduce_kernel(const NvArgs a)
 {
-    constexpr int UNROLL = WIRE_F32 ? 4 : 8;              // 16-byte loads in flight per thread: 8
+    constexpr int RUNS = WIRE_F32 ? EFA_NV_LOADS / 2 : EFA_NV_LOADS;     // runs per warp and iteration
     __shared__ int abort_word;
     if (threadIdx.x == 0) {
         abort_word = 0;
-        block_barrier(a, a.target_start, 61, &abort_word);
+        block_barrier(a.flags_mc, a.flags_uc, a.limit_ns, a.target_start, 61, &abort_word);
     }
     __syncthreads();
     if (abort_word == 0) {
-        // this rank's share of the range
-        const size_t per = (a.n16 + a.R - 1) / a.R;
+        // this rank's share of the range, in whole runs (32 units of 8 elements) except at the end of the range
+        const size_t per = ((a.n16 + a.R - 1) / a.R + 31) / 32 * 32;
         const size_t lo = min((size_t)a.rank * per, a.n16), hi = min(lo + per, a.n16);
-        const size_t stride = (size_t)gridDim.x * NV_THREADS;
-        for (size_t i = lo + (size_t)blockIdx.x * NV_THREADS + threadIdx.x; i < hi; i += UNROLL * stride) {
-            uint4 v[UNROLL];
+        const int lane = threadIdx.x & 31;
+        const size_t warp = (size_t)blockIdx.x * (NV_THREADS / 32) + (threadIdx.x >> 5);
+        const size_t warps = (size_t)gridDim.x * (NV_THREADS / 32);
+        const int my_unit = WIRE_F32 ? ((lane & 1) ? 16 + (lane >> 1) : (lane >> 1)) : lane;   // the unit this lane stores
+        for (size_t run = lo + warp * 32; run < hi; run += RUNS * warps * 32) {
+            uint4 v[RUNS];
             #pragma unroll
-            for (int u = 0; u < UNROLL; u++) {
-                const size_t e = a.first16 + i + u * stride;
-                if (i + u * stride < hi) {
-                    if (WIRE_F32) {
-                        const uint4 x = multimem_ld_reduce_f32(a.mc_send + e * 32);
-                        const uint4 y = multimem_ld_reduce_f32(a.mc_send + e * 32 + 16);
-                        v[u].x = pack_f16x2(__uint_as_float(x.x), __uint_as_float(x.y));
-                        v[u].y = pack_f16x2(__uint_as_float(x.z), __uint_as_float(x.w));
-                        v[u].z = pack_f16x2(__uint_as_float(y.x), __uint_as_float(y.y));
-                        v[u].w = pack_f16x2(__uint_as_float(y.z), __uint_as_float(y.w));
-                    } else {
-                        v[u] = multimem_ld_reduce_f16(a.mc_send + e * 16);
-                    }
+            for (int u = 0; u < RUNS; u++) {
+                const size_t base = run + (size_t)u * warps * 32;          // first unit of the run
+                v[u] = make_uint4(0u, 0u, 0u, 0u);
+                if (base >= hi) continue;                                  // the same for the whole warp
+                const int left = (int)min((size_t)32, hi - base);          // units of this run inside the share
+                if (WIRE_F32) {
+                    const char* src = a.mc_send + (a.first16 + base) * 32;
+                    uint4 x = make_uint4(0u, 0u, 0u, 0u), y = x;
+                    if ((lane >> 1) < left)      x = multimem_ld_reduce_f32(src + lane * 16);
+                    if (16 + (lane >> 1) < left) y = multimem_ld_reduce_f32(src + 512 + lane * 16);
+                    v[u].x = pack_f16x2(__uint_as_float(x.x), __uint_as_float(x.y));
+                    v[u].y = pack_f16x2(__uint_as_float(x.z), __uint_as_float(x.w));
+                    v[u].z = pack_f16x2(__uint_as_float(y.x), __uint_as_float(y.y));
+                    v[u].w = pack_f16x2(__uint_as_float(y.z), __uint_as_float(y.w));
+                } else if (lane < left) {
+                    v[u] = multimem_ld_reduce_f16(a.mc_send + (a.first16 + base + lane) * 16);
                 }
             }
             #pragma unroll
-            for (int u = 0; u < UNROLL; u++)
-                if (i + u * stride < hi) multimem_st(a.mc_out + (a.first16 + i + u * stride) * 16, v[u]);
+            for (int u = 0; u < RUNS; u++) {
+                const size_t base = run + (size_t)u * warps * 32;
+                if (base >= hi) continue;
+                const int left = (int)min((size_t)32, hi - base);
+                uint4 out = v[u];
+                if (WIRE_F32) {
+                    // an even lane keeps its first half and takes the neighbour's first half; an odd lane the second halves
+                    const bool odd = lane & 1;
+                    const unsigned give0 = odd ? v[u].x : v[u].z, give1 = odd ? v[u].y : v[u].w;
+                    const unsigned got0 = __shfl_xor_sync(0xffffffffu, give0, 1), got1 = __shfl_xor_sync(0xffffffffu, give1, 1);
+                    out = odd ? make_uint4(got0, got1, v[u].z, v[u].w) : make_uint4(v[u].x, v[u].y, got0, got1);
+                }
+                if (my_unit < left) multimem_st(a.mc_out + (a.first16 + base + my_unit) * 16, out);
+            }
         }
     }
     __syncthreads();
     if (threadIdx.x == 0) {
         // Arrive even after a failed first barrier, so that the flags stay in step across ranks.
         int second = 0;
-        block_barrier(a, a.target_end, 62, abort_word == 0 ? &abort_word : &second);
+        block_barrier(a.flags_mc, a.flags_uc, a.limit_ns, a.target_end, 62, abort_word == 0 ? &abort_word : &second);
+        if (abort_word != 0 && a.status != nullptr && atomicCAS(a.status, 0, (int)KS_WAIT_TIMEOUT) == 0) {
+            a.status[1] = (int)blockIdx.x;
+            a.status[2] = abort_word;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// The same reduction with the sum done on the SM: rank r fetches its share of EVERY rank's fp32 partial sums
+// (its own among them) with bulk asynchronous copies into shared memory, adds them in rank order, rounds once and
+// stores the fp16 result to every rank through the switch (multimem.st). A bulk copy moves 8 KB per instruction and
+// a block keeps up to 192 KB in flight, so a dozen blocks fill the links, where multimem.ld_reduce (a round trip
+// through the switch per 16 bytes and thread) needs some fifty. The price is wire bytes: each link carries
+// (R-1)/R of the fp32 partial sums inbound instead of 1/R.
+// Warp 0 issues the copies (one elected lane), warps 1-4 add and store; ring of `nstage` stages, every wait bounded.
+// ---------------------------------------------------------------------------------------------
+constexpr int PL_THREADS = 160;
+constexpr int PL_CONSUMERS = 128;
+constexpr int PL_UNITS = 256;                              // units of 8 elements per chunk: 8 KB of fp32 per rank
+constexpr int PL_CHUNK_BYTES = PL_UNITS * 32;
+constexpr int PL_MAX_STAGES = 8;
+constexpr int PL_SMEM_BUDGET = 192 * 1024;
+
+struct PullArgs {
+    const float* send_peer[8]; // every rank's partial sums (peer mappings; this rank's own at [rank])
+    char*       mc_out;        // multicast view of the result buffers
+    unsigned*   flags_mc;
+    const unsigned* flags_uc;
+    size_t      first16, n16;  // range in units of 8 elements
+    int         R, rank, nstage;
+    unsigned    target_start, target_end;
+    unsigned long long limit_ns;
+    int*        status;
+};
+
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 :: "r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
+__global__ void __launch_bounds__(PL_THREADS)
+pull_allreduce_kernel(const PullArgs a)
+{
+    extern __shared__ __align__(128) unsigned char pl_smem[];
+    __shared__ uint64_t full[PL_MAX_STAGES], empty[PL_MAX_STAGES];
+    __shared__ int abort_word;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        abort_word = 0;
+        for (int s = 0; s < a.nstage; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], PL_CONSUMERS / 32); }
+        mbar_fence_init();
+        block_barrier(a.flags_mc, a.flags_uc, a.limit_ns, a.target_start, 63, &abort_word);
+    }
+    __syncthreads();
+    if (abort_word == 0) {
+        // this rank's share of the range, in whole chunks except at the end of the range
+        const size_t per = ((a.n16 + a.R - 1) / a.R + PL_UNITS - 1) / PL_UNITS * PL_UNITS;
+        const size_t lo = min((size_t)a.rank * per, a.n16), hi = min(lo + per, a.n16);
+        const int nchunks = (int)((hi - lo + PL_UNITS - 1) / PL_UNITS);
+        const size_t stage_bytes = (size_t)a.R * PL_CHUNK_BYTES;
+        if (warp == 0) {
+            if (elect_one()) {
+                // the partial sums were written through the generic proxy (on this GPU and on the peers) and are read
+                // through the asynchronous one
+                asm volatile("fence.proxy.async;" ::: "memory");
+                int it = 0, s = 0, use = 0;
+                for (int k = blockIdx.x; k < nchunks; k += gridDim.x, it++) {
+                    if (use > 0 && !mbar_wait(&empty[s], (uint32_t)((use - 1) & 1), &abort_word, 64, a.limit_ns)) break;
+                    const size_t unit0 = lo + (size_t)k * PL_UNITS;
+                    const uint32_t bytes = (uint32_t)min((size_t)PL_UNITS, hi - unit0) * 32u;
+                    mbar_expect_tx(&full[s], bytes * (uint32_t)a.R);
+                    unsigned char* dst = pl_smem + (size_t)s * stage_bytes;
+                    for (int q = 0; q < a.R; q++) {
+                        int j = a.rank + 1 + q; if (j >= a.R) j -= a.R;      // every rank starts at another peer
+                        bulk_load(dst + (size_t)q * PL_CHUNK_BYTES, a.send_peer[j] + (a.first16 + unit0) * 8, bytes, &full[s]);
+                    }
+                    if (++s == a.nstage) { s = 0; use++; }
+                }
+                if (abort_word != 0) {
+                    // somebody gave up: no copy may still be on its way into this block's shared memory when it exits
+                    for (int t = 0; t < a.nstage; t++) {
+                        const int uses = use + (t < s ? 1 : 0);              // copies issued into stage t so far
+                        int local = 0;
+                        if (uses > 0) mbar_wait(&full[t], (uint32_t)((uses - 1) & 1), &local, 0, a.limit_ns);
+                    }
+                }
+            }
+        } else {
+            const int t = threadIdx.x - 32;
+            int s = 0, use = 0;
+            for (int k = blockIdx.x; k < nchunks; k += gridDim.x) {
+                if (!mbar_wait(&full[s], (uint32_t)(use & 1), &abort_word, 65, a.limit_ns)) break;
+                const size_t unit0 = lo + (size_t)k * PL_UNITS;
+                const int units = (int)min((size_t)PL_UNITS, hi - unit0);
+                const unsigned char* src = pl_smem + (size_t)s * stage_bytes;
+                for (int unit = t; unit < units; unit += PL_CONSUMERS) {
+                    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                    for (int j = 0; j < a.R; j++) {                          // rank order: the same sum whoever adds
+                        int q = j - a.rank - 1; if (q < 0) q += a.R;
+                        const float4* p = reinterpret_cast<const float4*>(src + (size_t)q * PL_CHUNK_BYTES + (size_t)unit * 32);
+                        const float4 x = p[0], y = p[1];
+                        acc[0] += x.x; acc[1] += x.y; acc[2] += x.z; acc[3] += x.w;
+                        acc[4] += y.x; acc[5] += y.y; acc[6] += y.z; acc[7] += y.w;
+                    }
+                    uint4 out;
+                    out.x = pack_f16x2(acc[0], acc[1]); out.y = pack_f16x2(acc[2], acc[3]);
+                    out.z = pack_f16x2(acc[4], acc[5]); out.w = pack_f16x2(acc[6], acc[7]);
+                    multimem_st(a.mc_out + (a.first16 + unit0 + unit) * 16, out);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[s]);
+                if (++s == a.nstage) { s = 0; use++; }
+            }
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int second = 0;
+        block_barrier(a.flags_mc, a.flags_uc, a.limit_ns, a.target_end, 66, abort_word == 0 ? &abort_word : &second);
         if (abort_word != 0 && a.status != nullptr && atomicCAS(a.status, 0, (int)KS_WAIT_TIMEOUT) == 0) {
             a.status[1] = (int)blockIdx.x;
             a.status[2] = abort_word;
@@ -262,8 +420,22 @@ bool all_ok(const efa_world& w, bool mine)
     return v == 0.0;
 }
 
+void release_pull(NvlsState* st)
+{
+    for (int r = 0; r < 8; r++) {
+        if (st->pull_opened[r]) cudaIpcCloseMemHandle(st->pull_opened[r]);
+        st->pull_opened[r] = nullptr;
+        st->pull_peer[r] = nullptr;
+    }
+    if (st->pull_send) cudaFree(st->pull_send);
+    st->pull_send = nullptr;
+    st->pull_bytes = 0;
+    (void)cudaGetLastError();
+}
+
 void release_local(NvlsState* st)
 {
+    release_pull(st);
     const DriverApi* api = driver_api();
     if (!api) return;
     if (st->mc_mapped) { api->cuMemUnmap(st->mcva, st->size); st->mc_mapped = false; }
@@ -357,6 +529,43 @@ int create_region(efa_ctx* c, NvlsState* st, size_t data_bytes)
     return 0;
 }
 
+// fp32 partial sums of the pulling reduction: one plain allocation per rank, mapped by every other rank.
+struct PullPacket {
+    cudaIpcMemHandle_t handle;
+    int ok;
+};
+
+int create_pull(efa_ctx* c, NvlsState* st, size_t bytes, int ctas)
+{
+    const efa_world& w = c->world;
+    const int R = w.size;
+    // A second bank of flags, all zero again: the pulling kernel's grid may differ from the in-switch kernel's.
+    st->pull_ctas = (ctas >= 1 && ctas <= NV_MAX_CTAS) ? ctas : 12;
+    for (unsigned& q : st->pull_seq) q = 0;
+    if (cudaMemset((unsigned*)st->uc + (size_t)EFA_MAX_COMM * NV_MAX_CTAS, 0, (size_t)EFA_MAX_COMM * NV_MAX_CTAS * sizeof(unsigned)) != cudaSuccess ||
+        cudaDeviceSynchronize() != cudaSuccess) { set_error("reduce=pull: clearing the flags failed"); return 1; }
+    if (world_barrier(w)) return 1;
+    bool ok = cudaMalloc(reinterpret_cast<void**>(&st->pull_send), bytes) == cudaSuccess;
+    if (ok) { st->pull_bytes = bytes; ok = cudaMemset(st->pull_send, 0, bytes) == cudaSuccess && cudaDeviceSynchronize() == cudaSuccess; }
+    PullPacket mine;
+    std::memset(&mine, 0, sizeof(mine));
+    mine.ok = ok && cudaIpcGetMemHandle(&mine.handle, st->pull_send) == cudaSuccess;
+    std::vector<PullPacket> all((size_t)R);
+    if (w.allgather_bytes(w.user, &mine, all.data(), sizeof(PullPacket))) { release_pull(st); set_error("reduce=pull: handle exchange failed"); return 1; }
+    bool every = true;
+    for (int r = 0; r < R; r++) every = every && all[(size_t)r].ok;
+    if (!every) { (void)cudaGetLastError(); release_pull(st); set_error("reduce=pull: a rank could not allocate or export %zu bytes of partial sums", bytes); return 1; }
+    bool opened = true;
+    for (int r = 0; r < R && opened; r++) {
+        if (r == w.rank) { st->pull_peer[r] = st->pull_send; continue; }
+        void* ptr = nullptr;
+        opened = cudaIpcOpenMemHandle(&ptr, all[(size_t)r].handle, cudaIpcMemLazyEnablePeerAccess) == cudaSuccess;
+        if (opened) { st->pull_opened[r] = ptr; st->pull_peer[r] = static_cast<float*>(ptr); }
+    }
+    if (!all_ok(w, opened)) { (void)cudaGetLastError(); release_pull(st); set_error("reduce=pull: a rank could not map a peer's partial sums (cudaIpcOpenMemHandle)"); return 5; }
+    return 0;
+}
+
 }  // namespace
 
 int nvls_supported(efa_ctx* c, const efa_params& p, const char** why)
@@ -376,24 +585,40 @@ int nvls_prepare(efa_ctx* c, const efa_params& p)
     if (!c->nvls) c->nvls = new NvlsState();
     NvlsState* st = c->nvls;
     const size_t want = (size_t)p.S * p.d * sizeof(__half);
+    const bool pull = p.reduce == EFA_REDUCE_PULL;
+    if (pull && c->world.size > 1 && !c->world.allgather_bytes) { set_error("reduce=pull needs the world's allgather_bytes callback"); return 2; }
     // Growing is collective, so the ranks vote (they all see the same params; the vote guards against a mix-up).
-    double vote = (st->size != 0 && st->data_bytes >= want && st->R == c->world.size) ? 0.0 : 1.0;
+    // A grid is fixed while its flags live, so an explicit reduce_ctas that differs from the grid in place rebuilds too.
+    const bool asked = p.reduce_ctas >= 1 && p.reduce_ctas <= NV_MAX_CTAS;
+    double vote = (st->size != 0 && st->data_bytes >= want && st->R == c->world.size &&
+                   (pull || !asked || p.reduce_ctas == c->nvls_ctas)) ? 0.0 : 1.0;
+    if (vote == 0.0 && pull && (st->pull_bytes < 2 * st->data_bytes || (asked && p.reduce_ctas != st->pull_ctas)))
+        vote = 0.5;                                         // the region is fine, the fp32 partial sums (or their grid) are not
     if (world_max(c->world, &vote)) return 1;
     if (vote == 0.0) return 0;
+    if (vote == 0.5) {
+        if (world_barrier(c->world)) return 1;
+        EFA_CUDA(cudaDeviceSynchronize());
+        release_pull(st);
+        return create_pull(c, st, 2 * st->data_bytes, p.reduce_ctas);
+    }
     if (world_barrier(c->world)) return 1;
     EFA_CUDA(cudaDeviceSynchronize());
     release_local(st);
     if (world_barrier(c->world)) return 1;
     const size_t data = (want + 4095) / 4096 * 4096;
     // The grid of the reduction kernel is fixed for the life of a region (flag b counts the barriers of block b).
-    c->nvls_ctas = (p.reduce_ctas >= 1 && p.reduce_ctas <= NV_MAX_CTAS) ? p.reduce_ctas : 16;
-    return create_region(c, st, data);
+    c->nvls_ctas = (!pull && p.reduce_ctas >= 1 && p.reduce_ctas <= NV_MAX_CTAS) ? p.reduce_ctas : 32;
+    if (create_region(c, st, data)) return 1;
+    return pull ? create_pull(c, st, 2 * st->data_bytes, p.reduce_ctas) : 0;
 }
+
+void* nvls_pull_send_buf(efa_ctx* c) { return c->nvls ? (void*)c->nvls->pull_send : nullptr; }
 
 void* nvls_send_buf(efa_ctx* c) { return c->nvls && c->nvls->size ? (void*)(c->nvls->uc + NV_FLAG_BYTES) : nullptr; }
 void* nvls_result_buf(efa_ctx* c) { return c->nvls && c->nvls->size ? (void*)(c->nvls->uc + NV_FLAG_BYTES + 2 * c->nvls->data_bytes) : nullptr; }
 
-int nvls_allreduce(efa_ctx* c, int slot, size_t first, size_t n, bool wire_f32, cudaStream_t stream)
+int nvls_allreduce(efa_ctx* c, int slot, size_t first, size_t n, bool wire_f32, bool pull, cudaStream_t stream)
 {
     NvlsState* st = c->nvls;
     if (!st || !st->size) { set_error("nvls_allreduce without nvls_prepare"); return 2; }
@@ -403,6 +628,32 @@ int nvls_allreduce(efa_ctx* c, int slot, size_t first, size_t n, bool wire_f32, 
         return 2;
     }
     if (n == 0) return 0;
+    if (pull) {
+        if (!st->pull_send) { set_error("nvls_allreduce: the pulling reduction was not prepared"); return 2; }
+        PullArgs q;
+        for (int r = 0; r < 8; r++) q.send_peer[r] = r < st->R ? st->pull_peer[r] : nullptr;
+        q.mc_out = (char*)(st->mcva + NV_FLAG_BYTES + 2 * st->data_bytes);
+        q.flags_mc = (unsigned*)st->mcva + (size_t)(EFA_MAX_COMM + slot) * NV_MAX_CTAS;
+        q.flags_uc = (const unsigned*)st->uc + (size_t)(EFA_MAX_COMM + slot) * NV_MAX_CTAS;
+        q.first16 = first / 8; q.n16 = n / 8;
+        q.R = st->R; q.rank = st->rank;
+        q.nstage = PL_SMEM_BUDGET / (st->R * PL_CHUNK_BYTES);
+        if (q.nstage > PL_MAX_STAGES) q.nstage = PL_MAX_STAGES;
+        q.target_start = (unsigned)st->R * (st->pull_seq[slot] + 1u);
+        q.target_end = (unsigned)st->R * (st->pull_seq[slot] + 2u);
+        st->pull_seq[slot] += 2u;
+        q.limit_ns = c->wait_limit_ns;
+        q.status = kernel_status_word();
+        const size_t smem = (size_t)q.nstage * st->R * PL_CHUNK_BYTES;
+        static bool configured = false;
+        if (!configured) {
+            EFA_CUDA(cudaFuncSetAttribute(pull_allreduce_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PL_SMEM_BUDGET));
+            configured = true;
+        }
+        pull_allreduce_kernel<<<st->pull_ctas, PL_THREADS, smem, stream>>>(q);
+        EFA_CUDA(cudaGetLastError());
+        return 0;
+    }
     NvArgs a;
     a.mc_send = (const char*)(st->mcva + NV_FLAG_BYTES);
     a.mc_out = (char*)(st->mcva + NV_FLAG_BYTES + 2 * st->data_bytes);
@@ -447,6 +698,6 @@ template <class K> int touch_kernel(K kernel)
 }
 }  // namespace
 
-int nvls_preload() { return touch_kernel(nvls_allreduce_kernel<true>) || touch_kernel(nvls_allreduce_kernel<false>); }
+int nvls_preload() { return touch_kernel(nvls_allreduce_kernel<true>) || touch_kernel(nvls_allreduce_kernel<false>) || touch_kernel(pull_allreduce_kernel); }
 
 }  // namespace efa

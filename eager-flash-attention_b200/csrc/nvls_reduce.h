@@ -19,12 +19,15 @@ int nvls_prepare(efa_ctx* c, const efa_params& p);
 // rows appear on every rank.
 void* nvls_send_buf(efa_ctx* c);
 void* nvls_result_buf(efa_ctx* c);
+void* nvls_pull_send_buf(efa_ctx* c);      // [S][d] fp32, plain device memory mapped by every rank (EFA_REDUCE_PULL)
 
 // Reduce elements [first, first + n) of the partial sums (fp32 when wire_f32, else fp16; the element index is the
 // same either way) over all ranks into the same elements of the fp16 result buffer of EVERY rank. One kernel on `stream`; `slot` (< EFA_MAX_COMM) names the stream's barrier flags, so
 // calls on different streams may overlap as long as they use different slots. Collective: every rank makes
 // the same sequence of calls per slot.
-int nvls_allreduce(efa_ctx* c, int slot, size_t first, size_t n, bool wire_f32, cudaStream_t stream);
+// pull: the partial sums are the fp32 ones at nvls_pull_send_buf (EFA_REDUCE_PULL): every rank fetches its share of all ranks'
+// partial sums over peer mappings, adds them itself and multicasts the result.
+int nvls_allreduce(efa_ctx* c, int slot, size_t first, size_t n, bool wire_f32, bool pull, cudaStream_t stream);
 
 // One file descriptor from rank 0 to every other rank of one host (Unix-domain socket, SCM_RIGHTS): rank 0 passes
 // fd_root and gets it back in *fd_out, the others receive a descriptor of their own for the same open file.

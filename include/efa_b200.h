@@ -147,8 +147,12 @@ int         efa_parse_mode(const char* s); /* parse_mode (run_drivers.cuh:20), -
  *   P2P:  stream mode only: one persistent kernel does projection and reduction over peer-mapped memory.
  *   NVLS: the NVSwitch sums the ranks' fp16 partial sums (fp32 accumulation, one rounding) through an NVLink
  *         multicast object; one small kernel per reduction on the communication stream. Needs a device and fabric
- *         with multicast support; otherwise the call fails with a message (nothing falls back silently). */
-enum { EFA_REDUCE_NCCL = 0, EFA_REDUCE_P2P = 1, EFA_REDUCE_NVLS = 2 };
+ *         with multicast support; otherwise the call fails with a message (nothing falls back silently).
+ *   PULL: every rank fetches its share of all ranks' fp32 partial sums over peer mappings with bulk asynchronous
+ *         copies, adds them in rank order, rounds once and multicasts the fp16 result through the switch. More
+ *         bytes per link than NVLS ((R-1)/R of the partial sums inbound instead of 1/R) for far fewer thread
+ *         blocks taken from the attention kernel. Same requirements as NVLS, plus CUDA IPC between the ranks. */
+enum { EFA_REDUCE_NCCL = 0, EFA_REDUCE_P2P = 1, EFA_REDUCE_NVLS = 2, EFA_REDUCE_PULL = 3 };
 
 enum { EFA_WIRE_AUTO = 0, EFA_WIRE_F16 = 1, EFA_WIRE_F32 = 2 };
 
