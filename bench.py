@@ -197,13 +197,16 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--mode", default="stream", choices=["stream", "megatron"])
-    ap.add_argument("--reduce", default="auto", choices=["auto", "nccl", "p2p", "nvls", "pull"],
+    ap.add_argument("--reduce", default="auto", choices=["auto", "nccl", "p2p", "nvls", "pull", "push"],
                     help="how the partial sums are reduced: NCCL AllReduce per group of tiles, the persistent "
                          "projection+reduction kernel over peer memory (stream mode), the NVSwitch through an NVLink "
                          "multicast object, or bulk copies of the peers' fp32 partial sums added on the SM and multicast "
                          "(pull); auto = the one that measured fastest for this rank count")
     ap.add_argument("--reduce-ctas", type=int, default=0,
                     help="thread blocks of the nvls / pull reduction kernel (0 = the library's default)")
+    ap.add_argument("--reserve-sms", type=int, default=0,
+                    help="stream mode: SMs the attention kernel leaves to the projection and the reduction (0 = none: it "
+                         "launches one block per work item and the others take SMs as its blocks retire)")
     ap.add_argument("--wire", default="auto", choices=["auto", "f16", "f32"],
                     help="element type of the partial sums on the links: the fp32 accumulators (auto), or fp16 (half the bytes, "
                          "one more rounding per partial sum)")
@@ -255,11 +258,12 @@ def main():
         raise SystemExit(f"invalid workload for {world_size} ranks: {why}")
     if args.reduce == "auto":
         args.reduce = REDUCE_BY_RANKS.get(world_size, "nccl")
-    p.reduce = dict(nccl=pkg.REDUCE_NCCL, p2p=pkg.REDUCE_P2P, nvls=pkg.REDUCE_NVLS, pull=pkg.REDUCE_PULL)[args.reduce]
+    p.reduce = dict(nccl=pkg.REDUCE_NCCL, p2p=pkg.REDUCE_P2P, nvls=pkg.REDUCE_NVLS, pull=pkg.REDUCE_PULL, push=pkg.REDUCE_PUSH)[args.reduce]
     p.row_order = dict(auto=pkg.ROWS_AUTO, asc=pkg.ROWS_ASCENDING, desc=pkg.ROWS_DESCENDING, mixed=pkg.ROWS_MIXED)[args.order]
     p.wire = dict(auto=pkg.WIRE_AUTO, f16=pkg.WIRE_F16, f32=pkg.WIRE_F32)[args.wire]
     p.group_tiles = args.group_tiles
     p.reduce_ctas = args.reduce_ctas
+    p.reserve_sms = args.reserve_sms
     mode = pkg.parse_mode(args.mode)
     descending = bool(pkg.stream_plan(p)[2])
 
@@ -276,7 +280,7 @@ def main():
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")      # > 126 MB L2
     weights = pkg.Weights(*(t.data_ptr() for t in dev))
     ctx = pkg.make_ctx(world, ncomm=W["ncomm"])
-    if args.reduce in ("nvls", "pull") and world_size > 1:
+    if args.reduce in ("nvls", "pull", "push") and world_size > 1:
         # the multicast reduction writes its result in place into the context's symmetric region
         class _Region:
             def __init__(self, ptr, shape):
@@ -375,7 +379,7 @@ def main():
             ms_per_step=ms, higher_is_better=False, scaling="strong", vs_baseline=None, dtype="f16 (f32 accumulate)",
             data="synthetic",
             config=dict(workload=f"S={p.S} H={p.H} d_h={p.d_h} causal tile={p.tile} ncomm={W['ncomm']} TP={world_size}",
-                        mode=args.mode, split=p.split, reduce=args.reduce, reduce_ctas=(args.reduce_ctas or "default"), wire=args.wire, row_order=args.order,
+                        mode=args.mode, split=p.split, reduce=args.reduce, reduce_ctas=(args.reduce_ctas or "default"), reserve_sms=args.reserve_sms, wire=args.wire, row_order=args.order,
                         group_tiles=args.group_tiles or "auto (S/8 rows per launch)",
                         l2="256 MB buffer written between steps",
                         e2e="pinned host Q/K/V/W_O copied in by every rank, the fp16 [S][d] result (identical on all ranks) copied "

@@ -27,6 +27,7 @@
 #include <sys/un.h>
 #include <unistd.h>
 
+#include <algorithm>
 #include <cstddef>
 #include <cstring>
 #include <vector>
@@ -45,6 +46,10 @@ struct NvlsState {
     size_t pull_bytes = 0;
     float* pull_peer[8] = {};
     void*  pull_opened[8] = {};      // what cudaIpcOpenMemHandle returned, per peer
+    // EFA_REDUCE_PUSH: R slabs of the same size, slab q receives rank q's partial sums of this rank's shares
+    float* push_stage = nullptr;
+    float* push_peer[8] = {};        // the peers' slabs (their mapping of push_stage)
+    void*  push_opened[8] = {};
     int    pull_ctas = 0;            // grid of the pulling kernel, fixed while these buffers live (it has flags and counts of its own)
     unsigned pull_seq[EFA_MAX_COMM] = {};
 };
@@ -204,10 +209,12 @@ nvls_allreduce_kernel(const NvArgs a)
 // a block keeps up to 192 KB in flight, so a dozen blocks fill the links, where multimem.ld_reduce (a round trip
 // through the switch per 16 bytes and thread) needs some fifty. The price is wire bytes: each link carries
 // (R-1)/R of the fp32 partial sums inbound instead of 1/R.
-// Warp 0 issues the copies (one elected lane), warps 1-4 add and store; ring of `nstage` stages, every wait bounded.
+// Warp 0 issues the copies (one elected lane), warps 1-8 add and store, one unit of 8 elements per thread and chunk;
+// ring of `nstage` stages, every wait bounded. With four adding warps the kernel was bound by them, not by the links:
+// fetching from local memory (the pushing variant) was no faster per block than fetching from a peer.
 // ---------------------------------------------------------------------------------------------
-constexpr int PL_THREADS = 160;
-constexpr int PL_CONSUMERS = 128;
+constexpr int PL_CONSUMERS = 256;
+constexpr int PL_THREADS = 32 + PL_CONSUMERS;
 constexpr int PL_UNITS = 256;                              // units of 8 elements per chunk: 8 KB of fp32 per rank
 constexpr int PL_CHUNK_BYTES = PL_UNITS * 32;
 constexpr int PL_MAX_STAGES = 8;
@@ -286,14 +293,25 @@ pull_allreduce_kernel(const PullArgs a)
                 const size_t unit0 = lo + (size_t)k * PL_UNITS;
                 const int units = (int)min((size_t)PL_UNITS, hi - unit0);
                 const unsigned char* src = pl_smem + (size_t)s * stage_bytes;
-                for (int unit = t; unit < units; unit += PL_CONSUMERS) {
+                static_assert(PL_UNITS == PL_CONSUMERS, "one unit per adding thread and chunk");
+                if (t < units) {
+                    const int unit = t;
+                    float4 x[8], y[8];
+                    #pragma unroll
+                    for (int j = 0; j < 8; j++) {                            // all loads first, then the sum in rank order
+                        if (j < a.R) {
+                            int q = j - a.rank - 1; if (q < 0) q += a.R;
+                            const float4* p = reinterpret_cast<const float4*>(src + (size_t)q * PL_CHUNK_BYTES + (size_t)unit * 32);
+                            x[j] = p[0]; y[j] = p[1];
+                        }
+                    }
                     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                    for (int j = 0; j < a.R; j++) {                          // rank order: the same sum whoever adds
-                        int q = j - a.rank - 1; if (q < 0) q += a.R;
-                        const float4* p = reinterpret_cast<const float4*>(src + (size_t)q * PL_CHUNK_BYTES + (size_t)unit * 32);
-                        const float4 x = p[0], y = p[1];
-                        acc[0] += x.x; acc[1] += x.y; acc[2] += x.z; acc[3] += x.w;
-                        acc[4] += y.x; acc[5] += y.y; acc[6] += y.z; acc[7] += y.w;
+                    #pragma unroll
+                    for (int j = 0; j < 8; j++) {                            // rank order: the same sum whoever adds
+                        if (j < a.R) {
+                            acc[0] += x[j].x; acc[1] += x[j].y; acc[2] += x[j].z; acc[3] += x[j].w;
+                            acc[4] += y[j].x; acc[5] += y[j].y; acc[6] += y[j].z; acc[7] += y[j].w;
+                        }
                     }
                     uint4 out;
                     out.x = pack_f16x2(acc[0], acc[1]); out.y = pack_f16x2(acc[2], acc[3]);
@@ -427,6 +445,13 @@ void release_pull(NvlsState* st)
         st->pull_opened[r] = nullptr;
         st->pull_peer[r] = nullptr;
     }
+    for (int r = 0; r < 8; r++) {
+        if (st->push_opened[r]) cudaIpcCloseMemHandle(st->push_opened[r]);
+        st->push_opened[r] = nullptr;
+        st->push_peer[r] = nullptr;
+    }
+    if (st->push_stage) cudaFree(st->push_stage);
+    st->push_stage = nullptr;
     if (st->pull_send) cudaFree(st->pull_send);
     st->pull_send = nullptr;
     st->pull_bytes = 0;
@@ -531,11 +556,12 @@ int create_region(efa_ctx* c, NvlsState* st, size_t data_bytes)
 
 // fp32 partial sums of the pulling reduction: one plain allocation per rank, mapped by every other rank.
 struct PullPacket {
-    cudaIpcMemHandle_t handle;
+    cudaIpcMemHandle_t handle, stage;
     int ok;
 };
 
-int create_pull(efa_ctx* c, NvlsState* st, size_t bytes, int ctas)
+// push: also the slabs that the peers' copy engines write this rank's shares into (R times `bytes`).
+int create_pull(efa_ctx* c, NvlsState* st, size_t bytes, int ctas, bool push)
 {
     const efa_world& w = c->world;
     const int R = w.size;
@@ -549,7 +575,9 @@ int create_pull(efa_ctx* c, NvlsState* st, size_t bytes, int ctas)
     if (ok) { st->pull_bytes = bytes; ok = cudaMemset(st->pull_send, 0, bytes) == cudaSuccess && cudaDeviceSynchronize() == cudaSuccess; }
     PullPacket mine;
     std::memset(&mine, 0, sizeof(mine));
+    if (ok && push) ok = cudaMalloc(reinterpret_cast<void**>(&st->push_stage), bytes * (size_t)R) == cudaSuccess;
     mine.ok = ok && cudaIpcGetMemHandle(&mine.handle, st->pull_send) == cudaSuccess;
+    if (mine.ok && push) mine.ok = cudaIpcGetMemHandle(&mine.stage, st->push_stage) == cudaSuccess;
     std::vector<PullPacket> all((size_t)R);
     if (w.allgather_bytes(w.user, &mine, all.data(), sizeof(PullPacket))) { release_pull(st); set_error("reduce=pull: handle exchange failed"); return 1; }
     bool every = true;
@@ -561,6 +589,11 @@ int create_pull(efa_ctx* c, NvlsState* st, size_t bytes, int ctas)
         void* ptr = nullptr;
         opened = cudaIpcOpenMemHandle(&ptr, all[(size_t)r].handle, cudaIpcMemLazyEnablePeerAccess) == cudaSuccess;
         if (opened) { st->pull_opened[r] = ptr; st->pull_peer[r] = static_cast<float*>(ptr); }
+        if (opened && push) {
+            ptr = nullptr;
+            opened = cudaIpcOpenMemHandle(&ptr, all[(size_t)r].stage, cudaIpcMemLazyEnablePeerAccess) == cudaSuccess;
+            if (opened) { st->push_opened[r] = ptr; st->push_peer[r] = static_cast<float*>(ptr); }
+        }
     }
     if (!all_ok(w, opened)) { (void)cudaGetLastError(); release_pull(st); set_error("reduce=pull: a rank could not map a peer's partial sums (cudaIpcOpenMemHandle)"); return 5; }
     return 0;
@@ -585,14 +618,15 @@ int nvls_prepare(efa_ctx* c, const efa_params& p)
     if (!c->nvls) c->nvls = new NvlsState();
     NvlsState* st = c->nvls;
     const size_t want = (size_t)p.S * p.d * sizeof(__half);
-    const bool pull = p.reduce == EFA_REDUCE_PULL;
+    const bool push = p.reduce == EFA_REDUCE_PUSH;
+    const bool pull = p.reduce == EFA_REDUCE_PULL || push;
     if (pull && c->world.size > 1 && !c->world.allgather_bytes) { set_error("reduce=pull needs the world's allgather_bytes callback"); return 2; }
     // Growing is collective, so the ranks vote (they all see the same params; the vote guards against a mix-up).
     // A grid is fixed while its flags live, so an explicit reduce_ctas that differs from the grid in place rebuilds too.
     const bool asked = p.reduce_ctas >= 1 && p.reduce_ctas <= NV_MAX_CTAS;
     double vote = (st->size != 0 && st->data_bytes >= want && st->R == c->world.size &&
                    (pull || !asked || p.reduce_ctas == c->nvls_ctas)) ? 0.0 : 1.0;
-    if (vote == 0.0 && pull && (st->pull_bytes < 2 * st->data_bytes || (asked && p.reduce_ctas != st->pull_ctas)))
+    if (vote == 0.0 && pull && (st->pull_bytes < 2 * st->data_bytes || (asked && p.reduce_ctas != st->pull_ctas) || (push && !st->push_stage)))
         vote = 0.5;                                         // the region is fine, the fp32 partial sums (or their grid) are not
     if (world_max(c->world, &vote)) return 1;
     if (vote == 0.0) return 0;
@@ -600,7 +634,7 @@ int nvls_prepare(efa_ctx* c, const efa_params& p)
         if (world_barrier(c->world)) return 1;
         EFA_CUDA(cudaDeviceSynchronize());
         release_pull(st);
-        return create_pull(c, st, 2 * st->data_bytes, p.reduce_ctas);
+        return create_pull(c, st, 2 * st->data_bytes, p.reduce_ctas, push);
     }
     if (world_barrier(c->world)) return 1;
     EFA_CUDA(cudaDeviceSynchronize());
@@ -610,7 +644,7 @@ int nvls_prepare(efa_ctx* c, const efa_params& p)
     // The grid of the reduction kernel is fixed for the life of a region (flag b counts the barriers of block b).
     c->nvls_ctas = (!pull && p.reduce_ctas >= 1 && p.reduce_ctas <= NV_MAX_CTAS) ? p.reduce_ctas : 32;
     if (create_region(c, st, data)) return 1;
-    return pull ? create_pull(c, st, 2 * st->data_bytes, p.reduce_ctas) : 0;
+    return pull ? create_pull(c, st, 2 * st->data_bytes, p.reduce_ctas, push) : 0;
 }
 
 void* nvls_pull_send_buf(efa_ctx* c) { return c->nvls ? (void*)c->nvls->pull_send : nullptr; }
@@ -618,8 +652,9 @@ void* nvls_pull_send_buf(efa_ctx* c) { return c->nvls ? (void*)c->nvls->pull_sen
 void* nvls_send_buf(efa_ctx* c) { return c->nvls && c->nvls->size ? (void*)(c->nvls->uc + NV_FLAG_BYTES) : nullptr; }
 void* nvls_result_buf(efa_ctx* c) { return c->nvls && c->nvls->size ? (void*)(c->nvls->uc + NV_FLAG_BYTES + 2 * c->nvls->data_bytes) : nullptr; }
 
-int nvls_allreduce(efa_ctx* c, int slot, size_t first, size_t n, bool wire_f32, bool pull, cudaStream_t stream)
+int nvls_allreduce(efa_ctx* c, int slot, size_t first, size_t n, bool wire_f32, int how, cudaStream_t stream)
 {
+    const bool pull = how != NVLS_IN_SWITCH, push = how == NVLS_PUSH;
     NvlsState* st = c->nvls;
     if (!st || !st->size) { set_error("nvls_allreduce without nvls_prepare"); return 2; }
     if (slot < 0 || slot >= EFA_MAX_COMM) { set_error("nvls_allreduce: slot %d out of range", slot); return 2; }
@@ -632,6 +667,24 @@ int nvls_allreduce(efa_ctx* c, int slot, size_t first, size_t n, bool wire_f32, 
         if (!st->pull_send) { set_error("nvls_allreduce: the pulling reduction was not prepared"); return 2; }
         PullArgs q;
         for (int r = 0; r < 8; r++) q.send_peer[r] = r < st->R ? st->pull_peer[r] : nullptr;
+        if (push) {
+            // The copy engines write this rank's partial sums of every peer's share into the peer's slab for this rank
+            // (posted writes, no thread block involved); the kernel below then finds all it adds in local memory. Its first
+            // barrier is passed once every rank has launched it, that is, once every rank's copies are complete.
+            if (!st->push_stage) { set_error("nvls_allreduce: the pushing reduction was not prepared"); return 2; }
+            const size_t n16 = n / 8, first16 = first / 8;
+            const size_t per = ((n16 + st->R - 1) / st->R + PL_UNITS - 1) / PL_UNITS * PL_UNITS;      // as in the kernel
+            const size_t slab = st->pull_bytes / sizeof(float);
+            for (int k = 1; k < st->R; k++) {
+                const int j = (st->rank + k) % st->R;                       // every rank starts at another peer
+                const size_t lo = std::min((size_t)j * per, n16), hi = std::min(lo + per, n16);
+                if (hi == lo) continue;
+                const size_t at = (first16 + lo) * 8;
+                EFA_CUDA(cudaMemcpyAsync(st->push_peer[j] + (size_t)st->rank * slab + at, st->pull_send + at, (hi - lo) * 32,
+                                         cudaMemcpyDeviceToDevice, stream));
+            }
+            for (int r = 0; r < st->R; r++) q.send_peer[r] = r == st->rank ? st->pull_send : st->push_stage + (size_t)r * slab;
+        }
         q.mc_out = (char*)(st->mcva + NV_FLAG_BYTES + 2 * st->data_bytes);
         q.flags_mc = (unsigned*)st->mcva + (size_t)(EFA_MAX_COMM + slot) * NV_MAX_CTAS;
         q.flags_uc = (const unsigned*)st->uc + (size_t)(EFA_MAX_COMM + slot) * NV_MAX_CTAS;

@@ -7,7 +7,7 @@ table behind the defaults costs seconds. Launch with torchrun, one rank per GPU:
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29511 \\
         eager-flash-attention_b200/sweep/reduce_sweep.py --out reduce_sweep_R8.csv
 
-Rows: mode, reduce, wire, order, reduce_ctas, mean / min ms of `--trials` steps (each the max over ranks, L2 flushed
+Rows: mode, reduce, wire, order, reduce_ctas, reserve_sms, mean / min ms of `--trials` steps (each the max over ranks, L2 flushed
 between steps), mean attention-kernel ms. Inputs N(0,1), seed 42, as the benchmark plan's configurations.
 """
 import argparse
@@ -47,8 +47,10 @@ def main():
     ap.add_argument("--trials", type=int, default=5)
     ap.add_argument("--only", default="", help="comma-separated reduce kinds to keep (default: all)")
     ap.add_argument("--out", default="")
-    ap.add_argument("--trace", default="", help="one more setting, 'mode,reduce,wire,order,reduce_ctas', whose last step prints "
-                                                "the per-group timeline of every rank (stderr)")
+    ap.add_argument("--settings", default="", help="instead of the built-in list: 'mode,reduce,wire,order,reduce_ctas[,reserve_sms]' "
+                                                   "entries separated by ';'")
+    ap.add_argument("--trace", default="", help="one more setting, same form, whose last step prints the per-group timeline "
+                                                "of every rank (stderr)")
     args = ap.parse_args()
 
     import torch
@@ -84,25 +86,32 @@ def main():
             self.__cuda_array_interface__ = dict(shape=shape, typestr="<f2", data=(ptr, False), version=2)
 
     keep = set(x for x in args.only.split(",") if x)
-    rows = ["mode,reduce,wire,order,reduce_ctas,ranks,mean_ms,min_ms,attn_kernel_ms,status"]
-    settings = [s + (False,) for s in DEFAULT_SETTINGS if not keep or s[1] in keep]
+    rows = ["mode,reduce,wire,order,reduce_ctas,reserve_sms,ranks,mean_ms,min_ms,attn_kernel_ms,status"]
+    def parse(text, traced):
+        f = text.split(",")
+        return (f[0], f[1], f[2], f[3], int(f[4]), int(f[5]) if len(f) > 5 else 0, traced)
+
+    if args.settings:
+        settings = [parse(t, False) for t in args.settings.split(";") if t]
+    else:
+        settings = [s + (0, False) for s in DEFAULT_SETTINGS if not keep or s[1] in keep]
     if args.trace:
-        m, r, w, o, n = args.trace.split(",")
-        settings.append((m, r, w, o, int(n), True))
-    for mode_s, reduce, wire, order, ctas, traced in settings:
+        settings.append(parse(args.trace, True))
+    for mode_s, reduce, wire, order, ctas, reserve, traced in settings:
         if world_size == 1 and reduce not in ("nccl", "none"):
             continue
         p.skip_comm = 1 if reduce == "none" else 0
-        p.reduce = dict(none=pkg.REDUCE_NCCL, nccl=pkg.REDUCE_NCCL, p2p=pkg.REDUCE_P2P, nvls=pkg.REDUCE_NVLS, pull=pkg.REDUCE_PULL)[reduce]
+        p.reduce = dict(none=pkg.REDUCE_NCCL, nccl=pkg.REDUCE_NCCL, p2p=pkg.REDUCE_P2P, nvls=pkg.REDUCE_NVLS, pull=pkg.REDUCE_PULL, push=pkg.REDUCE_PUSH)[reduce]
         p.wire = dict(auto=pkg.WIRE_AUTO, f16=pkg.WIRE_F16, f32=pkg.WIRE_F32)[wire]
         p.row_order = dict(auto=pkg.ROWS_AUTO, asc=pkg.ROWS_ASCENDING, desc=pkg.ROWS_DESCENDING, mixed=pkg.ROWS_MIXED)[order]
         p.reduce_ctas = ctas
+        p.reserve_sms = reserve
         mode = pkg.parse_mode(mode_s)
         status = "ok"
         ts, ks = [], []
         try:
             out = own_out
-            if reduce in ("nvls", "pull") and world_size > 1:
+            if reduce in ("nvls", "pull", "push") and world_size > 1:
                 out = torch.as_tensor(_Region(pkg.nvls_output(ctx, p), (p.S, p.d)), device="cuda")
             pkg.kernel_status_reset()
             for i in range(args.warmup + args.trials):
@@ -125,7 +134,7 @@ def main():
             dist.all_reduce(bad, op=dist.ReduceOp.MAX)
         if int(bad[0]) and status == "ok":
             status = "failed on another rank"
-        rows.append(f"{mode_s},{reduce},{wire},{order},{ctas},{world_size},"
+        rows.append(f"{mode_s},{reduce},{wire},{order},{ctas},{reserve},{world_size},"
                     f"{statistics.mean(ts) if ts else float('nan'):.4f},{min(ts) if ts else float('nan'):.4f},"
                     f"{statistics.mean(ks) if ks else float('nan'):.4f},{status}")
         if rank == 0:
