@@ -197,7 +197,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--mode", default="stream", choices=["stream", "megatron"])
-    ap.add_argument("--reduce", default="auto", choices=["auto", "nccl", "p2p", "nvls", "pull", "push"],
+    ap.add_argument("--reduce", default="auto", choices=["auto", "nccl", "p2p", "nvls", "pull"],
                     help="how the partial sums are reduced: NCCL AllReduce per group of tiles, the persistent "
                          "projection+reduction kernel over peer memory (stream mode), the NVSwitch through an NVLink "
                          "multicast object, or bulk copies of the peers' fp32 partial sums added on the SM and multicast "
@@ -258,7 +258,7 @@ def main():
         raise SystemExit(f"invalid workload for {world_size} ranks: {why}")
     if args.reduce == "auto":
         args.reduce = REDUCE_BY_RANKS.get(world_size, "nccl")
-    p.reduce = dict(nccl=pkg.REDUCE_NCCL, p2p=pkg.REDUCE_P2P, nvls=pkg.REDUCE_NVLS, pull=pkg.REDUCE_PULL, push=pkg.REDUCE_PUSH)[args.reduce]
+    p.reduce = dict(nccl=pkg.REDUCE_NCCL, p2p=pkg.REDUCE_P2P, nvls=pkg.REDUCE_NVLS, pull=pkg.REDUCE_PULL)[args.reduce]
     p.row_order = dict(auto=pkg.ROWS_AUTO, asc=pkg.ROWS_ASCENDING, desc=pkg.ROWS_DESCENDING, mixed=pkg.ROWS_MIXED)[args.order]
     p.wire = dict(auto=pkg.WIRE_AUTO, f16=pkg.WIRE_F16, f32=pkg.WIRE_F32)[args.wire]
     p.group_tiles = args.group_tiles
@@ -280,7 +280,7 @@ def main():
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")      # > 126 MB L2
     weights = pkg.Weights(*(t.data_ptr() for t in dev))
     ctx = pkg.make_ctx(world, ncomm=W["ncomm"])
-    if args.reduce in ("nvls", "pull", "push") and world_size > 1:
+    if args.reduce in ("nvls", "pull") and world_size > 1:
         # the multicast reduction writes its result in place into the context's symmetric region
         class _Region:
             def __init__(self, ptr, shape):

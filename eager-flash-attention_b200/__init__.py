@@ -26,7 +26,7 @@ LIB_PATH = os.environ.get("EFA_B200_LIB") or os.path.join(_HERE, "libefa_b200.so
 F32, F16 = 0, 1
 MODE_ATTN, MODE_ATTN_TILED, MODE_MEGATRON, MODE_SYNC, MODE_OVERLAP, MODE_STREAM, MODE_COMM = range(7)
 MODE_NAMES = ("attn", "attn_tiled", "megatron", "sync", "overlap", "stream", "comm")
-REDUCE_NCCL, REDUCE_P2P, REDUCE_NVLS, REDUCE_PULL, REDUCE_PUSH = 0, 1, 2, 3, 4
+REDUCE_NCCL, REDUCE_P2P, REDUCE_NVLS, REDUCE_PULL = 0, 1, 2, 3
 ROWS_AUTO, ROWS_ASCENDING, ROWS_DESCENDING, ROWS_MIXED = 0, 1, 2, 3
 WIRE_AUTO, WIRE_F16, WIRE_F32 = 0, 1, 2
 RECIPE_REF, RECIPE_NORMAL = 0, 1

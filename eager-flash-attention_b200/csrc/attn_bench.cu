@@ -96,7 +96,7 @@ static void usage(const char* prog)
         "          [--nbuf 2] [--split 1] [--ncomm 1] [--warmup 3] [--trials 10]\n"
         "          [--modes attn,attn_tiled,megatron,sync,overlap,stream,comm] [--no-header]\n"
         "          [--causal] [--proj fp16|fp32] [--no_prio] [--no_proj] [--no_comm]\n"
-        "          [--reduce nccl|p2p|nvls|pull|push] [--group_tiles 0] [--order auto|asc|desc|mixed] [--data normal|ref] [--seed 42] [--residual]\n"
+        "          [--reduce nccl|p2p|nvls|pull] [--group_tiles 0] [--order auto|asc|desc|mixed] [--data normal|ref] [--seed 42] [--residual]\n"
         "          [--wire auto|f16|f32] [--band_rows 0] [--reserve_sms 0] [--reduce_ctas 0] [--trace] [--own_output]\n", prog);
 }
 
@@ -173,8 +173,7 @@ int main(int argc, char** argv)
     if (std::strcmp(reduce, "p2p") == 0) p.reduce = EFA_REDUCE_P2P;
     else if (std::strcmp(reduce, "nvls") == 0) p.reduce = EFA_REDUCE_NVLS;
     else if (std::strcmp(reduce, "pull") == 0) p.reduce = EFA_REDUCE_PULL;
-    else if (std::strcmp(reduce, "push") == 0) p.reduce = EFA_REDUCE_PUSH;
-    else if (std::strcmp(reduce, "nccl") != 0) fail("--reduce must be nccl, p2p, nvls, pull or push");
+    else if (std::strcmp(reduce, "nccl") != 0) fail("--reduce must be nccl, p2p, nvls or pull");
     if (order_s == "asc") p.row_order = EFA_ROWS_ASCENDING;
     else if (order_s == "desc") p.row_order = EFA_ROWS_DESCENDING;
     else if (order_s == "mixed") p.row_order = EFA_ROWS_MIXED;
@@ -207,7 +206,7 @@ int main(int argc, char** argv)
     CUDA_OK(cudaMalloc(&dw.W_O, wo_n * 2));
     // With the multicast reduction the output lives in the context's symmetric region, where the switch writes it in
     // place; --own_output keeps the reference's arrangement (the caller's cudaMalloc, one extra device copy per reduction).
-    const bool symmetric_out = (p.reduce == EFA_REDUCE_NVLS || p.reduce == EFA_REDUCE_PULL || p.reduce == EFA_REDUCE_PUSH) && world > 1 && !p.skip_comm && !cl.on("--own_output");
+    const bool symmetric_out = (p.reduce == EFA_REDUCE_NVLS || p.reduce == EFA_REDUCE_PULL) && world > 1 && !p.skip_comm && !cl.on("--own_output");
     if (symmetric_out) EFA_OK(efa_nvls_output(ctx, &p, &output));
     else CUDA_OK(cudaMalloc(&output, out_n * (proj_f32 ? 4 : 2)));
     CUDA_OK(cudaMemcpy(dw.Qh, hq.data(), qkv_n * 2, cudaMemcpyHostToDevice));

@@ -142,7 +142,7 @@ extern "C" int efa_run_mode_host_rows(efa_ctx* c, int mode,
     }
     // Device result: the multicast region's result buffer when the switch reduces (written in place), else staging.
     void* dev_out = nullptr;
-    const bool nvls = (p->reduce == EFA_REDUCE_NVLS || p->reduce == EFA_REDUCE_PULL || p->reduce == EFA_REDUCE_PUSH) && p->R > 1 && !p->skip_comm;
+    const bool nvls = (p->reduce == EFA_REDUCE_NVLS || p->reduce == EFA_REDUCE_PULL) && p->R > 1 && !p->skip_comm;
     if (nvls) { if (efa_nvls_output(c, p, &dev_out)) return 1; }
     else { if (ensure_bytes(&c->h_out, &c->h_out_bytes, ob)) return 1; dev_out = c->h_out; }
     if (mode == EFA_MODE_STREAM && p->causal && !p->skip_proj && p->reduce != EFA_REDUCE_P2P) {

@@ -27,7 +27,6 @@
 #include <sys/un.h>
 #include <unistd.h>
 
-#include <algorithm>
 #include <cstddef>
 #include <cstring>
 #include <vector>
@@ -46,10 +45,6 @@ struct NvlsState {
     size_t pull_bytes = 0;
     float* pull_peer[8] = {};
     void*  pull_opened[8] = {};      // what cudaIpcOpenMemHandle returned, per peer
-    // EFA_REDUCE_PUSH: R slabs of the same size, slab q receives rank q's partial sums of this rank's shares
-    float* push_stage = nullptr;
-    float* push_peer[8] = {};        // the peers' slabs (their mapping of push_stage)
-    void*  push_opened[8] = {};
     int    pull_ctas = 0;            // grid of the pulling kernel, fixed while these buffers live (it has flags and counts of its own)
     unsigned pull_seq[EFA_MAX_COMM] = {};
 };
@@ -210,8 +205,7 @@ nvls_allreduce_kernel(const NvArgs a)
 // through the switch per 16 bytes and thread) needs some fifty. The price is wire bytes: each link carries
 // (R-1)/R of the fp32 partial sums inbound instead of 1/R.
 // Warp 0 issues the copies (one elected lane), warps 1-8 add and store, one unit of 8 elements per thread and chunk;
-// ring of `nstage` stages, every wait bounded. With four adding warps the kernel was bound by them, not by the links:
-// fetching from local memory (the pushing variant) was no faster per block than fetching from a peer.
+// ring of `nstage` stages, every wait bounded.
 // ---------------------------------------------------------------------------------------------
 constexpr int PL_CONSUMERS = 256;
 constexpr int PL_THREADS = 32 + PL_CONSUMERS;
@@ -445,13 +439,6 @@ void release_pull(NvlsState* st)
         st->pull_opened[r] = nullptr;
         st->pull_peer[r] = nullptr;
     }
-    for (int r = 0; r < 8; r++) {
-        if (st->push_opened[r]) cudaIpcCloseMemHandle(st->push_opened[r]);
-        st->push_opened[r] = nullptr;
-        st->push_peer[r] = nullptr;
-    }
-    if (st->push_stage) cudaFree(st->push_stage);
-    st->push_stage = nullptr;
     if (st->pull_send) cudaFree(st->pull_send);
     st->pull_send = nullptr;
     st->pull_bytes = 0;
@@ -556,12 +543,11 @@ int create_region(efa_ctx* c, NvlsState* st, size_t data_bytes)
 
 // fp32 partial sums of the pulling reduction: one plain allocation per rank, mapped by every other rank.
 struct PullPacket {
-    cudaIpcMemHandle_t handle, stage;
+    cudaIpcMemHandle_t handle;
     int ok;
 };
 
-// push: also the slabs that the peers' copy engines write this rank's shares into (R times `bytes`).
-int create_pull(efa_ctx* c, NvlsState* st, size_t bytes, int ctas, bool push)
+int create_pull(efa_ctx* c, NvlsState* st, size_t bytes, int ctas)
 {
     const efa_world& w = c->world;
     const int R = w.size;
@@ -575,9 +561,7 @@ int create_pull(efa_ctx* c, NvlsState* st, size_t bytes, int ctas, bool push)
     if (ok) { st->pull_bytes = bytes; ok = cudaMemset(st->pull_send, 0, bytes) == cudaSuccess && cudaDeviceSynchronize() == cudaSuccess; }
     PullPacket mine;
     std::memset(&mine, 0, sizeof(mine));
-    if (ok && push) ok = cudaMalloc(reinterpret_cast<void**>(&st->push_stage), bytes * (size_t)R) == cudaSuccess;
     mine.ok = ok && cudaIpcGetMemHandle(&mine.handle, st->pull_send) == cudaSuccess;
-    if (mine.ok && push) mine.ok = cudaIpcGetMemHandle(&mine.stage, st->push_stage) == cudaSuccess;
     std::vector<PullPacket> all((size_t)R);
     if (w.allgather_bytes(w.user, &mine, all.data(), sizeof(PullPacket))) { release_pull(st); set_error("reduce=pull: handle exchange failed"); return 1; }
     bool every = true;
@@ -589,11 +573,6 @@ int create_pull(efa_ctx* c, NvlsState* st, size_t bytes, int ctas, bool push)
         void* ptr = nullptr;
         opened = cudaIpcOpenMemHandle(&ptr, all[(size_t)r].handle, cudaIpcMemLazyEnablePeerAccess) == cudaSuccess;
         if (opened) { st->pull_opened[r] = ptr; st->pull_peer[r] = static_cast<float*>(ptr); }
-        if (opened && push) {
-            ptr = nullptr;
-            opened = cudaIpcOpenMemHandle(&ptr, all[(size_t)r].stage, cudaIpcMemLazyEnablePeerAccess) == cudaSuccess;
-            if (opened) { st->push_opened[r] = ptr; st->push_peer[r] = static_cast<float*>(ptr); }
-        }
     }
     if (!all_ok(w, opened)) { (void)cudaGetLastError(); release_pull(st); set_error("reduce=pull: a rank could not map a peer's partial sums (cudaIpcOpenMemHandle)"); return 5; }
     return 0;
@@ -618,15 +597,14 @@ int nvls_prepare(efa_ctx* c, const efa_params& p)
     if (!c->nvls) c->nvls = new NvlsState();
     NvlsState* st = c->nvls;
     const size_t want = (size_t)p.S * p.d * sizeof(__half);
-    const bool push = p.reduce == EFA_REDUCE_PUSH;
-    const bool pull = p.reduce == EFA_REDUCE_PULL || push;
+    const bool pull = p.reduce == EFA_REDUCE_PULL;
     if (pull && c->world.size > 1 && !c->world.allgather_bytes) { set_error("reduce=pull needs the world's allgather_bytes callback"); return 2; }
     // Growing is collective, so the ranks vote (they all see the same params; the vote guards against a mix-up).
     // A grid is fixed while its flags live, so an explicit reduce_ctas that differs from the grid in place rebuilds too.
     const bool asked = p.reduce_ctas >= 1 && p.reduce_ctas <= NV_MAX_CTAS;
     double vote = (st->size != 0 && st->data_bytes >= want && st->R == c->world.size &&
                    (pull || !asked || p.reduce_ctas == c->nvls_ctas)) ? 0.0 : 1.0;
-    if (vote == 0.0 && pull && (st->pull_bytes < 2 * st->data_bytes || (asked && p.reduce_ctas != st->pull_ctas) || (push && !st->push_stage)))
+    if (vote == 0.0 && pull && (st->pull_bytes < 2 * st->data_bytes || (asked && p.reduce_ctas != st->pull_ctas))) 
         vote = 0.5;                                         // the region is fine, the fp32 partial sums (or their grid) are not
     if (world_max(c->world, &vote)) return 1;
     if (vote == 0.0) return 0;
@@ -634,7 +612,7 @@ int nvls_prepare(efa_ctx* c, const efa_params& p)
         if (world_barrier(c->world)) return 1;
         EFA_CUDA(cudaDeviceSynchronize());
         release_pull(st);
-        return create_pull(c, st, 2 * st->data_bytes, p.reduce_ctas, push);
+        return create_pull(c, st, 2 * st->data_bytes, p.reduce_ctas);
     }
     if (world_barrier(c->world)) return 1;
     EFA_CUDA(cudaDeviceSynchronize());
@@ -644,7 +622,7 @@ int nvls_prepare(efa_ctx* c, const efa_params& p)
     // The grid of the reduction kernel is fixed for the life of a region (flag b counts the barriers of block b).
     c->nvls_ctas = (!pull && p.reduce_ctas >= 1 && p.reduce_ctas <= NV_MAX_CTAS) ? p.reduce_ctas : 32;
     if (create_region(c, st, data)) return 1;
-    return pull ? create_pull(c, st, 2 * st->data_bytes, p.reduce_ctas, push) : 0;
+    return pull ? create_pull(c, st, 2 * st->data_bytes, p.reduce_ctas) : 0;
 }
 
 void* nvls_pull_send_buf(efa_ctx* c) { return c->nvls ? (void*)c->nvls->pull_send : nullptr; }
@@ -652,9 +630,8 @@ void* nvls_pull_send_buf(efa_ctx* c) { return c->nvls ? (void*)c->nvls->pull_sen
 void* nvls_send_buf(efa_ctx* c) { return c->nvls && c->nvls->size ? (void*)(c->nvls->uc + NV_FLAG_BYTES) : nullptr; }
 void* nvls_result_buf(efa_ctx* c) { return c->nvls && c->nvls->size ? (void*)(c->nvls->uc + NV_FLAG_BYTES + 2 * c->nvls->data_bytes) : nullptr; }
 
-int nvls_allreduce(efa_ctx* c, int slot, size_t first, size_t n, bool wire_f32, int how, cudaStream_t stream)
+int nvls_allreduce(efa_ctx* c, int slot, size_t first, size_t n, bool wire_f32, bool pull, cudaStream_t stream)
 {
-    const bool pull = how != NVLS_IN_SWITCH, push = how == NVLS_PUSH;
     NvlsState* st = c->nvls;
     if (!st || !st->size) { set_error("nvls_allreduce without nvls_prepare"); return 2; }
     if (slot < 0 || slot >= EFA_MAX_COMM) { set_error("nvls_allreduce: slot %d out of range", slot); return 2; }
@@ -667,24 +644,6 @@ int nvls_allreduce(efa_ctx* c, int slot, size_t first, size_t n, bool wire_f32, 
         if (!st->pull_send) { set_error("nvls_allreduce: the pulling reduction was not prepared"); return 2; }
         PullArgs q;
         for (int r = 0; r < 8; r++) q.send_peer[r] = r < st->R ? st->pull_peer[r] : nullptr;
-        if (push) {
-            // The copy engines write this rank's partial sums of every peer's share into the peer's slab for this rank
-            // (posted writes, no thread block involved); the kernel below then finds all it adds in local memory. Its first
-            // barrier is passed once every rank has launched it, that is, once every rank's copies are complete.
-            if (!st->push_stage) { set_error("nvls_allreduce: the pushing reduction was not prepared"); return 2; }
-            const size_t n16 = n / 8, first16 = first / 8;
-            const size_t per = ((n16 + st->R - 1) / st->R + PL_UNITS - 1) / PL_UNITS * PL_UNITS;      // as in the kernel
-            const size_t slab = st->pull_bytes / sizeof(float);
-            for (int k = 1; k < st->R; k++) {
-                const int j = (st->rank + k) % st->R;                       // every rank starts at another peer
-                const size_t lo = std::min((size_t)j * per, n16), hi = std::min(lo + per, n16);
-                if (hi == lo) continue;
-                const size_t at = (first16 + lo) * 8;
-                EFA_CUDA(cudaMemcpyAsync(st->push_peer[j] + (size_t)st->rank * slab + at, st->pull_send + at, (hi - lo) * 32,
-                                         cudaMemcpyDeviceToDevice, stream));
-            }
-            for (int r = 0; r < st->R; r++) q.send_peer[r] = r == st->rank ? st->pull_send : st->push_stage + (size_t)r * slab;
-        }
         q.mc_out = (char*)(st->mcva + NV_FLAG_BYTES + 2 * st->data_bytes);
         q.flags_mc = (unsigned*)st->mcva + (size_t)(EFA_MAX_COMM + slot) * NV_MAX_CTAS;
         q.flags_uc = (const unsigned*)st->uc + (size_t)(EFA_MAX_COMM + slot) * NV_MAX_CTAS;

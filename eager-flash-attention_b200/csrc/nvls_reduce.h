@@ -25,11 +25,9 @@ void* nvls_pull_send_buf(efa_ctx* c);      // [S][d] fp32, plain device memory m
 // same either way) over all ranks into the same elements of the fp16 result buffer of EVERY rank. One kernel on `stream`; `slot` (< EFA_MAX_COMM) names the stream's barrier flags, so
 // calls on different streams may overlap as long as they use different slots. Collective: every rank makes
 // the same sequence of calls per slot.
-// how: NVLS_IN_SWITCH as described; NVLS_PULL / NVLS_PUSH take the fp32 partial sums at nvls_pull_send_buf, every rank adds
-// its share of all ranks' partial sums itself and multicasts the result. PULL fetches them over peer mappings inside the
-// kernel; PUSH has the copy engines deliver them beforehand (copies enqueued on `stream` ahead of the kernel).
-enum { NVLS_IN_SWITCH = 0, NVLS_PULL = 1, NVLS_PUSH = 2 };
-int nvls_allreduce(efa_ctx* c, int slot, size_t first, size_t n, bool wire_f32, int how, cudaStream_t stream);
+// pull: the partial sums are the fp32 ones at nvls_pull_send_buf (EFA_REDUCE_PULL): every rank fetches its share of all ranks'
+// partial sums over peer mappings, adds them itself and multicasts the result.
+int nvls_allreduce(efa_ctx* c, int slot, size_t first, size_t n, bool wire_f32, bool pull, cudaStream_t stream);
 
 // One file descriptor from rank 0 to every other rank of one host (Unix-domain socket, SCM_RIGHTS): rank 0 passes
 // fd_root and gets it back in *fd_out, the others receive a descriptor of their own for the same open file.

@@ -80,12 +80,12 @@ struct Run {
     {
         if (p.proj_f32) return true;
         if (p.skip_comm || p.R == 1 || p.reduce == EFA_REDUCE_P2P) return false;
-        if (p.reduce == EFA_REDUCE_PULL || p.reduce == EFA_REDUCE_PUSH) return true;   // these add fp32 partial sums only
+        if (p.reduce == EFA_REDUCE_PULL) return true;            // the pulling reduction adds fp32 partial sums only
         return p.wire != EFA_WIRE_F16;
     }
     // both reductions that deliver through the NVLink multicast region
-    bool nvls() const { return (p.reduce == EFA_REDUCE_NVLS || p.reduce == EFA_REDUCE_PULL || p.reduce == EFA_REDUCE_PUSH) && !p.skip_comm && p.R > 1; }
-    bool pull() const { return (p.reduce == EFA_REDUCE_PULL || p.reduce == EFA_REDUCE_PUSH) && nvls(); }
+    bool nvls() const { return (p.reduce == EFA_REDUCE_NVLS || p.reduce == EFA_REDUCE_PULL) && !p.skip_comm && p.R > 1; }
+    bool pull() const { return p.reduce == EFA_REDUCE_PULL && nvls(); }
     size_t send_row_bytes() const { return (size_t)p.d * (wire_f32() ? sizeof(float) : sizeof(__half)); }
     char* send_base() const { return static_cast<char*>(pull() ? nvls_pull_send_buf(c) : nvls() ? nvls_send_buf(c) : c->send_buf); }
 
@@ -142,9 +142,7 @@ struct Run {
             const bool f32 = wire_f32();
             const size_t first = (size_t)(static_cast<char*>(send) - send_base()) / (f32 ? sizeof(float) : sizeof(__half));
             launches++;
-            const int how = p.reduce == EFA_REDUCE_PUSH ? NVLS_PUSH : p.reduce == EFA_REDUCE_PULL ? NVLS_PULL : NVLS_IN_SWITCH;
-            if (how == NVLS_PUSH) launches += p.R - 1;                  // copies, not kernels, but counted as work enqueued
-            if (nvls_allreduce(c, slot, first, n, f32, how, cs)) return 1;
+            if (nvls_allreduce(c, slot, first, n, f32, pull(), cs)) return 1;
             char* landed = static_cast<char*>(nvls_result_buf(c)) + first * sizeof(__half);
             if (landed != static_cast<char*>(recv))      // an output inside the region (efa_nvls_output) is written in place
                 EFA_CUDA(cudaMemcpyAsync(recv, landed, n * sizeof(__half), cudaMemcpyDeviceToDevice, cs));
@@ -648,11 +646,11 @@ int run_mode_impl(efa_ctx* c, int mode, const efa_weights& w, void* output, cons
         set_error("run_mode: fp32 partial sums (proj_f32) go with the NCCL reduction and without a residual");
         return 2;
     }
-    if (p.reduce != EFA_REDUCE_NCCL && p.reduce != EFA_REDUCE_P2P && p.reduce != EFA_REDUCE_NVLS && p.reduce != EFA_REDUCE_PULL && p.reduce != EFA_REDUCE_PUSH) {
+    if (p.reduce != EFA_REDUCE_NCCL && p.reduce != EFA_REDUCE_P2P && p.reduce != EFA_REDUCE_NVLS && p.reduce != EFA_REDUCE_PULL) {
         set_error("run_mode: unknown reduction %d", p.reduce);
         return 2;
     }
-    if ((p.reduce == EFA_REDUCE_NVLS || p.reduce == EFA_REDUCE_PULL || p.reduce == EFA_REDUCE_PUSH) && p.R > 1 && !p.skip_comm) {
+    if ((p.reduce == EFA_REDUCE_NVLS || p.reduce == EFA_REDUCE_PULL) && p.R > 1 && !p.skip_comm) {
         const char* why = nullptr;
         if (!nvls_supported(c, p, &why)) { set_error("%s", why); return 5; }
     }

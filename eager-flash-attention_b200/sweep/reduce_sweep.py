@@ -101,7 +101,7 @@ def main():
         if world_size == 1 and reduce not in ("nccl", "none"):
             continue
         p.skip_comm = 1 if reduce == "none" else 0
-        p.reduce = dict(none=pkg.REDUCE_NCCL, nccl=pkg.REDUCE_NCCL, p2p=pkg.REDUCE_P2P, nvls=pkg.REDUCE_NVLS, pull=pkg.REDUCE_PULL, push=pkg.REDUCE_PUSH)[reduce]
+        p.reduce = dict(none=pkg.REDUCE_NCCL, nccl=pkg.REDUCE_NCCL, p2p=pkg.REDUCE_P2P, nvls=pkg.REDUCE_NVLS, pull=pkg.REDUCE_PULL)[reduce]
         p.wire = dict(auto=pkg.WIRE_AUTO, f16=pkg.WIRE_F16, f32=pkg.WIRE_F32)[wire]
         p.row_order = dict(auto=pkg.ROWS_AUTO, asc=pkg.ROWS_ASCENDING, desc=pkg.ROWS_DESCENDING, mixed=pkg.ROWS_MIXED)[order]
         p.reduce_ctas = ctas
@@ -111,7 +111,7 @@ def main():
         ts, ks = [], []
         try:
             out = own_out
-            if reduce in ("nvls", "pull", "push") and world_size > 1:
+            if reduce in ("nvls", "pull") and world_size > 1:
                 out = torch.as_tensor(_Region(pkg.nvls_output(ctx, p), (p.S, p.d)), device="cuda")
             pkg.kernel_status_reset()
             for i in range(args.warmup + args.trials):

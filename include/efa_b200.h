@@ -151,11 +151,8 @@ int         efa_parse_mode(const char* s); /* parse_mode (run_drivers.cuh:20), -
  *   PULL: every rank fetches its share of all ranks' fp32 partial sums over peer mappings with bulk asynchronous
  *         copies, adds them in rank order, rounds once and multicasts the fp16 result through the switch. More
  *         bytes per link than NVLS ((R-1)/R of the partial sums inbound instead of 1/R) for far fewer thread
- *         blocks taken from the attention kernel. Same requirements as NVLS, plus CUDA IPC between the ranks.
- *   PUSH: as PULL, but the partial sums travel by copy engine: every rank copies its partial sums of each peer's share
- *         into a slab in the peer's memory (posted writes, no thread block), and the adding kernel reads local memory
- *         only. Costs R times the partial sums in staging memory per rank. */
-enum { EFA_REDUCE_NCCL = 0, EFA_REDUCE_P2P = 1, EFA_REDUCE_NVLS = 2, EFA_REDUCE_PULL = 3, EFA_REDUCE_PUSH = 4 };
+ *         blocks taken from the attention kernel. Same requirements as NVLS, plus CUDA IPC between the ranks. */
+enum { EFA_REDUCE_NCCL = 0, EFA_REDUCE_P2P = 1, EFA_REDUCE_NVLS = 2, EFA_REDUCE_PULL = 3 };
 
 enum { EFA_WIRE_AUTO = 0, EFA_WIRE_F16 = 1, EFA_WIRE_F32 = 2 };
 
