@@ -103,23 +103,26 @@ def golden_cases():
     for line in open(man):
         if line.startswith("#") or not line.strip():
             continue
-        name, S, d, H, causal, seed, mx = line.split()
-        out.append((name, int(S), int(d), int(H), int(causal), int(seed), float(mx)))
+        f = line.split()
+        name, S, d, H, causal, seed, mx = f[:7]
+        ranks = int(f[7]) if len(f) > 7 else 1
+        out.append((name, int(S), int(d), int(H), int(causal), int(seed), float(mx), ranks))
     return out
 
 
 def test_golden_vectors_present():
-    assert len(golden_cases()) >= 4, "tests/golden/manifest.txt is missing or incomplete"
+    assert len(golden_cases()) >= 7, "tests/golden/manifest.txt is missing or incomplete"
+    assert sorted(set(c[7] for c in golden_cases())) == [1, 2, 4, 8]
 
 
 @pytest.mark.parametrize("case", golden_cases(), ids=lambda c: c[0])
 def test_oracle_matches_reference_gpu_checker(oracle, case):
     """The reference's checker works on the fp32 Q/K/V (attn_tests.cu:37); so does this comparison.
-    Differences are fp32 GEMM rounding only (cuBLAS SGEMM vs double accumulation)."""
-    name, S, d, H, causal, seed, mx = case
+    Differences are fp32 GEMM rounding only (cuBLAS SGEMM vs double accumulation). Cases with several ranks are the
+    sum of the ranks' partial blocks (rank-specific inputs, head shares), as the checker sums them."""
+    name, S, d, H, causal, seed, mx, ranks = case
     gold = np.fromfile(os.path.join(GOLDEN, name + ".f32"), np.float32).reshape(S, d)
     assert abs(np.abs(gold).max() - mx) <= 1e-6 * max(mx, 1.0)
-    Q, K, V, W = oracle.ref_inputs(S, d, H, 1, 0, seed)
-    got = oracle.block_rows([(Q, K, V, W)], d, causal)
+    got = oracle.block_rows([oracle.ref_inputs(S, d, H, ranks, r, seed) for r in range(ranks)], d, causal)
     max_abs, max_ref = oracle.compare(got, gold)
     assert max_abs / max_ref < 2e-5, (max_abs, max_ref)
