@@ -60,6 +60,32 @@ def attention_flops(S, d_h, H_local, causal):
     return 4.0 * 64 * 64 * d_h * H_local * nb * (nb + 1) / 2
 
 
+def bind_near_gpu(device_index):
+    """Run this process on the CPUs of the GPU's NUMA node, so that the pinned host buffers it allocates next are
+    first touched there: with several ranks on one host, copies from the far socket's memory halve the PCIe rate each
+    GPU sees. Returns the node, or None where the topology cannot be read (nothing is changed then)."""
+    try:
+        import torch
+        pr = torch.cuda.get_device_properties(device_index)
+        bdf = f"{pr.pci_domain_id:04x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+        with open(f"/sys/bus/pci/devices/{bdf}/numa_node") as f:
+            node = int(f.read())
+        if node < 0:
+            return None
+        cpus = set()
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            for part in f.read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = os.sched_getaffinity(0) & cpus
+        if len(allowed) < 4:
+            return None
+        os.sched_setaffinity(0, allowed)
+        return node
+    except Exception:
+        return None
+
+
 class ClockSampler:
     """SM clock and throttle-reason samples taken DURING the timed region (NVML, every 5 ms, in a thread of
     this process; `nvidia-smi -lms` cannot sample a region of a few tens of milliseconds)."""
@@ -241,6 +267,7 @@ def main():
     pkg = entry.load_package()
     pkg.lib()                                   # fails loudly when the CUDA library is not built
     torch.cuda.set_device(local_rank)
+    numa_node = bind_near_gpu(local_rank)
     if world_size > 1:
         dist.init_process_group(backend="cpu:gloo,cuda:nccl", device_id=torch.device("cuda", local_rank))
         world = pkg.World.from_torch(None, local_device=local_rank)
@@ -379,7 +406,7 @@ def main():
             ms_per_step=ms, higher_is_better=False, scaling="strong", vs_baseline=None, dtype="f16 (f32 accumulate)",
             data="synthetic",
             config=dict(workload=f"S={p.S} H={p.H} d_h={p.d_h} causal tile={p.tile} ncomm={W['ncomm']} TP={world_size}",
-                        mode=args.mode, split=p.split, reduce=args.reduce, reduce_ctas=(args.reduce_ctas or "default"), reserve_sms=args.reserve_sms, wire=args.wire, row_order=args.order,
+                        mode=args.mode, split=p.split, reduce=args.reduce, reduce_ctas=(args.reduce_ctas or "default"), reserve_sms=args.reserve_sms, numa_node=numa_node, wire=args.wire, row_order=args.order,
                         group_tiles=args.group_tiles or "auto (S/8 rows per launch)",
                         l2="256 MB buffer written between steps",
                         e2e="pinned host Q/K/V/W_O copied in by every rank, the fp16 [S][d] result (identical on all ranks) copied "
