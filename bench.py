@@ -256,7 +256,7 @@ def main():
     if args.impl == "reference":
         line = run_reference(args, world_size, rank)
         if line is not None:
-            print(json.dumps(line), flush=True)
+            emit(line)
         return 0
 
     import numpy as np
@@ -438,9 +438,22 @@ def main():
         dist.barrier()
         dist.destroy_process_group()
     if line is not None:
-        print(json.dumps(line), flush=True)
+        emit(line)
     return 0
 
 
+_RESULT_FD = 1
+
+
+def emit(line):
+    """The one JSON line, on the process's original standard output."""
+    os.write(_RESULT_FD, (json.dumps(line) + "\n").encode())
+
+
 if __name__ == "__main__":
+    # Libraries print to standard output too (NCCL announces its version there): everything but the result line goes to
+    # standard error, so that standard output carries exactly one line.
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
     sys.exit(main())

@@ -35,6 +35,35 @@ DEFAULT_SETTINGS = [
 ]
 
 
+MODES = ("attn", "megatron", "sync", "overlap", "stream")
+REDUCES = ("none", "nccl", "p2p", "nvls", "pull")
+WIRES = ("auto", "f16", "f32")
+ORDERS = ("auto", "asc", "desc", "mixed")
+
+
+def parse_setting(text, traced=False):
+    """'mode,reduce,wire,order,reduce_ctas[,reserve_sms]' -> (mode, reduce, wire, order, ctas, reserve, traced)."""
+    f = [x.strip() for x in text.split(",")]
+    if len(f) not in (5, 6):
+        raise ValueError(f"setting {text!r}: five or six comma-separated fields expected")
+    if f[0] not in MODES or f[1] not in REDUCES or f[2] not in WIRES or f[3] not in ORDERS:
+        raise ValueError(f"setting {text!r}: unknown mode, reduction, wire type or row order")
+    return (f[0], f[1], f[2], f[3], int(f[4]), int(f[5]) if len(f) == 6 else 0, traced)
+
+
+def plan(settings_text="", only="", trace_text=""):
+    """The settings to time, in order: the built-in list (optionally only some reductions) or the given ones, then the
+    traced one."""
+    keep = set(x for x in only.split(",") if x)
+    if settings_text:
+        out = [parse_setting(t) for t in settings_text.split(";") if t.strip()]
+    else:
+        out = [s + (0, False) for s in DEFAULT_SETTINGS if not keep or s[1] in keep]
+    if trace_text:
+        out.append(parse_setting(trace_text, True))
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--S", type=int, default=32768)
@@ -85,18 +114,8 @@ def main():
         def __init__(self, ptr, shape):
             self.__cuda_array_interface__ = dict(shape=shape, typestr="<f2", data=(ptr, False), version=2)
 
-    keep = set(x for x in args.only.split(",") if x)
     rows = ["mode,reduce,wire,order,reduce_ctas,reserve_sms,ranks,mean_ms,min_ms,attn_kernel_ms,status"]
-    def parse(text, traced):
-        f = text.split(",")
-        return (f[0], f[1], f[2], f[3], int(f[4]), int(f[5]) if len(f) > 5 else 0, traced)
-
-    if args.settings:
-        settings = [parse(t, False) for t in args.settings.split(";") if t]
-    else:
-        settings = [s + (0, False) for s in DEFAULT_SETTINGS if not keep or s[1] in keep]
-    if args.trace:
-        settings.append(parse(args.trace, True))
+    settings = plan(args.settings, args.only, args.trace)
     for mode_s, reduce, wire, order, ctas, reserve, traced in settings:
         if world_size == 1 and reduce not in ("nccl", "none"):
             continue

@@ -69,3 +69,35 @@ def test_overlap_suite_names_its_environment():
     assert any(l.startswith("NCCL_MAX_CTAS=8 ") and "--reserve_sms 16" in l for l in lines)
     assert any("--no_comm" in l for l in lines) and any("--split 4" in l for l in lines) and any("--reduce p2p" in l for l in lines)
     assert any("--reduce nvls" in l for l in lines) and any("--order desc" in l for l in lines)
+
+
+def test_reduce_sweep_settings():
+    """reduce_sweep.py: the built-in list, a filter by reduction, explicit settings with and without reserved SMs, the
+    traced setting last; malformed settings are refused before any GPU work."""
+    import pytest
+    sys.path.insert(0, SWEEP)
+    import reduce_sweep
+    builtin = reduce_sweep.plan()
+    assert len(builtin) == len(reduce_sweep.DEFAULT_SETTINGS) and all(len(s) == 7 and s[5] == 0 and not s[6] for s in builtin)
+    assert {s[1] for s in builtin} == {"none", "nccl", "nvls", "pull", "p2p"}
+    assert {s[1] for s in reduce_sweep.plan(only="pull,nccl")} == {"pull", "nccl"}
+    got = reduce_sweep.plan("stream,pull,f32,asc,12;stream,pull,f32,asc,12,16;", trace_text="stream,nvls,f16,mixed,32")
+    assert got == [("stream", "pull", "f32", "asc", 12, 0, False), ("stream", "pull", "f32", "asc", 12, 16, False),
+                   ("stream", "nvls", "f16", "mixed", 32, 0, True)]
+    for bad in ("stream,pull,f32,asc", "stream,push,f32,asc,4", "stream,pull,f64,asc,4", "stream,pull,f32,up,4"):
+        with pytest.raises(ValueError):
+            reduce_sweep.parse_setting(bad)
+
+
+def test_committed_sweep_results_parse():
+    """The CSVs under sweep/results are what the tables in the notes quote: they must stay readable by the tools."""
+    sys.path.insert(0, SWEEP)
+    import cost_model
+    res = os.path.join(SWEEP, "results")
+    for name, lo, hi in (("comm_R2_pull.csv", 300e6, 600e6), ("comm_R2_nccl.csv", 250e6, 500e6)):
+        alpha, beta = cost_model.fit_allreduce(cost_model.read_rows(os.path.join(res, name)), 4)
+        assert 0.005 < alpha < 0.1 and lo < beta < hi, (name, alpha, beta)       # ms, bytes per ms
+    for name in ("reduce_sweep_R8_builtin_settings.csv", "reduce_sweep_R8_reserved_sms.csv", "reduce_sweep_R2_builtin_settings.csv"):
+        lines = open(os.path.join(res, name)).read().strip().splitlines()
+        assert lines[0].startswith("mode,reduce,wire,order,reduce_ctas") and len(lines) > 5
+        assert all(l.endswith(",ok") for l in lines[1:])
