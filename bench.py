@@ -283,7 +283,9 @@ def main():
     why = pkg.attn_check_params(p)
     if why:
         raise SystemExit(f"invalid workload for {world_size} ranks: {why}")
-    if args.reduce == "auto":
+    chosen_by_table = args.reduce == "auto"
+    reduce_note = None
+    if chosen_by_table:
         args.reduce = REDUCE_BY_RANKS.get(world_size, "nccl")
     p.reduce = dict(nccl=pkg.REDUCE_NCCL, p2p=pkg.REDUCE_P2P, nvls=pkg.REDUCE_NVLS, pull=pkg.REDUCE_PULL)[args.reduce]
     p.row_order = dict(auto=pkg.ROWS_AUTO, asc=pkg.ROWS_ASCENDING, desc=pkg.ROWS_DESCENDING, mixed=pkg.ROWS_MIXED)[args.order]
@@ -312,7 +314,18 @@ def main():
         class _Region:
             def __init__(self, ptr, shape):
                 self.__cuda_array_interface__ = dict(shape=shape, typestr="<f2", data=(ptr, False), version=2)
-        out = torch.as_tensor(_Region(pkg.nvls_output(ctx, p), (p.S, p.d)), device="cuda")
+        try:
+            out = torch.as_tensor(_Region(pkg.nvls_output(ctx, p), (p.S, p.d)), device="cuda")
+        except pkg.EfaError as e:
+            # Setting up the multicast region is collective and fails on every rank alike (no NVLink multicast on this
+            # machine, no CUDA IPC between the ranks). A reduction named on the command line fails here; the one taken
+            # from the table is replaced by NCCL, and the line says so.
+            if not chosen_by_table:
+                raise
+            reduce_note = f"nccl, because {args.reduce} could not be set up: {e}"
+            args.reduce = "nccl"
+            p.reduce = pkg.REDUCE_NCCL
+            out = torch.zeros((p.S, p.d), dtype=torch.float16, device="cuda")
     else:
         out = torch.zeros((p.S, p.d), dtype=torch.float16, device="cuda")
 
@@ -406,7 +419,7 @@ def main():
             ms_per_step=ms, higher_is_better=False, scaling="strong", vs_baseline=None, dtype="f16 (f32 accumulate)",
             data="synthetic",
             config=dict(workload=f"S={p.S} H={p.H} d_h={p.d_h} causal tile={p.tile} ncomm={W['ncomm']} TP={world_size}",
-                        mode=args.mode, split=p.split, reduce=args.reduce, reduce_ctas=(args.reduce_ctas or "default"), reserve_sms=args.reserve_sms, numa_node=numa_node, wire=args.wire, row_order=args.order,
+                        mode=args.mode, split=p.split, reduce=(reduce_note or args.reduce), reduce_ctas=(args.reduce_ctas or "default"), reserve_sms=args.reserve_sms, numa_node=numa_node, wire=args.wire, row_order=args.order,
                         group_tiles=args.group_tiles or "auto (S/8 rows per launch)",
                         l2="256 MB buffer written between steps",
                         e2e="pinned host Q/K/V/W_O copied in by every rank, the fp16 [S][d] result (identical on all ranks) copied "

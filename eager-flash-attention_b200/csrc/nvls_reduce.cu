@@ -1,4 +1,4 @@
-// Sum AllReduce of the fp16 partial sums through an NVLink multicast object.
+// Sum AllReduce of the partial sums (fp32 or fp16) through an NVLink multicast object.
 //
 // Stands in for allreduce() of eager-flash-attention (run_drivers.cu:26-30: ncclAllReduce, fp32 sum) on
 // one NVSwitch box. Every rank owns a region of the same size and layout (symmetric memory) that is
@@ -16,7 +16,8 @@
 // "every rank's share has landed everywhere".
 //
 // Waits are bounded: on expiry the block records a status and returns without touching the data.
-// No TMA, no cluster multicast; the multicast here is the NVSwitch one (multimem.*).
+// The multicast here is the NVSwitch one (multimem.*). The in-switch kernel uses no TMA at all; the pulling kernel
+// further down fetches with plain bulk asynchronous copies (one destination block each, no multicast qualifier).
 #include "nvls_reduce.h"
 
 #include "host_util.h"
@@ -554,10 +555,12 @@ int create_pull(efa_ctx* c, NvlsState* st, size_t bytes, int ctas)
     // A second bank of flags, all zero again: the pulling kernel's grid may differ from the in-switch kernel's.
     st->pull_ctas = (ctas >= 1 && ctas <= NV_MAX_CTAS) ? ctas : 12;
     for (unsigned& q : st->pull_seq) q = 0;
-    if (cudaMemset((unsigned*)st->uc + (size_t)EFA_MAX_COMM * NV_MAX_CTAS, 0, (size_t)EFA_MAX_COMM * NV_MAX_CTAS * sizeof(unsigned)) != cudaSuccess ||
-        cudaDeviceSynchronize() != cudaSuccess) { set_error("reduce=pull: clearing the flags failed"); return 1; }
-    if (world_barrier(w)) return 1;
-    bool ok = cudaMalloc(reinterpret_cast<void**>(&st->pull_send), bytes) == cudaSuccess;
+    // Every local failure up to the exchange travels in the packet's `ok`, so that all ranks return together; the
+    // exchange is also the barrier between clearing the flags and their first use.
+    bool ok = cudaMemset((unsigned*)st->uc + (size_t)EFA_MAX_COMM * NV_MAX_CTAS, 0,
+                         (size_t)EFA_MAX_COMM * NV_MAX_CTAS * sizeof(unsigned)) == cudaSuccess &&
+              cudaDeviceSynchronize() == cudaSuccess;
+    if (ok) ok = cudaMalloc(reinterpret_cast<void**>(&st->pull_send), bytes) == cudaSuccess;
     if (ok) { st->pull_bytes = bytes; ok = cudaMemset(st->pull_send, 0, bytes) == cudaSuccess && cudaDeviceSynchronize() == cudaSuccess; }
     PullPacket mine;
     std::memset(&mine, 0, sizeof(mine));
@@ -566,7 +569,7 @@ int create_pull(efa_ctx* c, NvlsState* st, size_t bytes, int ctas)
     if (w.allgather_bytes(w.user, &mine, all.data(), sizeof(PullPacket))) { release_pull(st); set_error("reduce=pull: handle exchange failed"); return 1; }
     bool every = true;
     for (int r = 0; r < R; r++) every = every && all[(size_t)r].ok;
-    if (!every) { (void)cudaGetLastError(); release_pull(st); set_error("reduce=pull: a rank could not allocate or export %zu bytes of partial sums", bytes); return 1; }
+    if (!every) { (void)cudaGetLastError(); release_pull(st); set_error("reduce=pull: a rank could not clear its flags, or allocate or export %zu bytes of partial sums", bytes); return 1; }
     bool opened = true;
     for (int r = 0; r < R && opened; r++) {
         if (r == w.rank) { st->pull_peer[r] = st->pull_send; continue; }
@@ -585,7 +588,7 @@ int nvls_supported(efa_ctx* c, const efa_params& p, const char** why)
     (void)c;
     *why = nullptr;
     if (p.R > 8) *why = "reduce=nvls handles at most 8 ranks (one NVSwitch box)";
-    else if (p.proj_f32) *why = "reduce=nvls sums fp16 partial sums (proj_f32 goes with the NCCL reduction)";
+    else if (p.proj_f32) *why = "reduce=nvls / pull write an fp16 result (proj_f32, an fp32 output, goes with the NCCL reduction)";
     return *why == nullptr;
 }
 
@@ -604,7 +607,7 @@ int nvls_prepare(efa_ctx* c, const efa_params& p)
     const bool asked = p.reduce_ctas >= 1 && p.reduce_ctas <= NV_MAX_CTAS;
     double vote = (st->size != 0 && st->data_bytes >= want && st->R == c->world.size &&
                    (pull || !asked || p.reduce_ctas == c->nvls_ctas)) ? 0.0 : 1.0;
-    if (vote == 0.0 && pull && (st->pull_bytes < 2 * st->data_bytes || (asked && p.reduce_ctas != st->pull_ctas))) 
+    if (vote == 0.0 && pull && (st->pull_bytes < 2 * st->data_bytes || (asked && p.reduce_ctas != st->pull_ctas)))
         vote = 0.5;                                         // the region is fine, the fp32 partial sums (or their grid) are not
     if (world_max(c->world, &vote)) return 1;
     if (vote == 0.0) return 0;
