@@ -142,10 +142,11 @@ const char* efa_mode_name(int mode);     /* mode_name  (run_drivers.cuh:19) */
 int         efa_parse_mode(const char* s); /* parse_mode (run_drivers.cuh:20), -1 if unknown */
 
 /* How the per-tile partial sums are reduced across ranks (allreduce, run_drivers.cu:26-30).
- *   NCCL: ncclAllReduce on communicator t % ncomm as the reference does; fp16 on the wire with two ranks, the fp32
- *         accumulators with more (NCCL adds fp16 in fp16, one rounding per hop), rounded once into the fp16 output.
+ *   NCCL: ncclAllReduce on communicator t % ncomm as the reference does, on the fp32 accumulators (ncclFloat) with one
+ *         conversion into the fp16 output afterwards; ncclHalf with wire = EFA_WIRE_F16 (NCCL then adds fp16 in fp16,
+ *         one rounding per hop).
  *   P2P:  stream mode only: one persistent kernel does projection and reduction over peer-mapped memory.
- *   NVLS: the NVSwitch sums the ranks' fp16 partial sums (fp32 accumulation, one rounding) through an NVLink
+ *   NVLS: the NVSwitch sums the ranks' partial sums (fp32; or fp16 with fp32 accumulation, one rounding) through an NVLink
  *         multicast object; one small kernel per reduction on the communication stream. Needs a device and fabric
  *         with multicast support; otherwise the call fails with a message (nothing falls back silently).
  *   PULL: every rank fetches its share of all ranks' fp32 partial sums over peer mappings with bulk asynchronous
