@@ -273,10 +273,14 @@ pull_allreduce_kernel(const PullArgs a)
                 }
                 if (abort_word != 0) {
                     // somebody gave up: no copy may still be on its way into this block's shared memory when it exits
+                    // (one limit for all stages together)
+                    const unsigned long long t_drain = globaltimer_ns();
                     for (int t = 0; t < a.nstage; t++) {
                         const int uses = use + (t < s ? 1 : 0);              // copies issued into stage t so far
+                        const unsigned long long spent = globaltimer_ns() - t_drain;
+                        if (spent >= a.limit_ns) break;
                         int local = 0;
-                        if (uses > 0) mbar_wait(&full[t], (uint32_t)((uses - 1) & 1), &local, 0, a.limit_ns);
+                        if (uses > 0) mbar_wait(&full[t], (uint32_t)((uses - 1) & 1), &local, 0, a.limit_ns - spent);
                     }
                 }
             }
