@@ -101,3 +101,25 @@ def test_committed_sweep_results_parse():
         lines = open(os.path.join(res, name)).read().strip().splitlines()
         assert lines[0].startswith("mode,reduce,wire,order,reduce_ctas") and len(lines) > 5
         assert all(l.endswith(",ok") for l in lines[1:])
+
+
+def test_reduce_sweep_table(tmp_path):
+    """bench_tables.py --reduce-sweep: one table per rank count, exposed communication against the run without a
+    reduction, attention-only and no-reduction rows in the heading only."""
+    sys.path.insert(0, SWEEP)
+    import bench_tables
+    p = tmp_path / "rs.csv"
+    p.write_text("mode,reduce,wire,order,reduce_ctas,reserve_sms,ranks,mean_ms,min_ms,attn_kernel_ms,status\n"
+                 "attn,nccl,auto,auto,0,0,8,1.0000,0.9900,0.9800,ok\n"
+                 "stream,none,auto,asc,0,0,8,1.5000,1.4900,1.4000,ok\n"
+                 "stream,pull,f32,asc,12,0,8,2.0000,1.9000,1.4500,ok\n"
+                 "megatron,pull,f32,auto,12,0,8,2.5000,2.4000,1.0000,ok\n"
+                 "stream,nvls,f32,asc,32,0,8,9.0000,9.0000,9.0000,error: x\n")
+    text = bench_tables.reduce_sweep_table(str(p))
+    assert "N = 8: attention only 1.000 ms, stream without a reduction 1.500 ms" in text
+    assert "| stream | pull | f32 | asc | 12 | 0 | 2.000 | 1.900 | 1.450 | 25 % |" in text
+    assert "| megatron | pull | f32 | auto | 12 | 0 | 2.500 | 2.400 | 1.000 |  |" in text
+    assert "nvls" not in text                       # failed settings are left out
+    # the committed results render
+    res = os.path.join(SWEEP, "results")
+    assert "| stream | pull | f32 | asc | 12 |" in bench_tables.reduce_sweep_table(os.path.join(res, "reduce_sweep_R8_reserved_sms.csv"))
