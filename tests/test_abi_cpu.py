@@ -164,3 +164,16 @@ def test_stream_plan_counts_without_a_buffer_and_rejects_a_short_one(pkg):
     buf = (pkg.StreamGroup * 4)()
     assert pkg.lib().efa_stream_plan(C.byref(p), buf, 4, None, None) == -1
     assert "groups" in pkg.last_error()
+
+
+def test_python_constants_match_the_header(pkg):
+    """Every enumerator of include/efa_b200.h that the ctypes mirror names has the header's value."""
+    text = open(os.path.join(ROOT, "include", "efa_b200.h")).read()
+    header = {m.group(1): int(m.group(2)) for m in re.finditer(r"\bEFA_([A-Z0-9_]+)\s*=\s*(\d+)", text)}
+    checked = 0
+    for name, value in vars(pkg).items():
+        if name.isupper() and isinstance(value, int) and name.split("_")[0] in ("REDUCE", "WIRE", "ROWS", "MODE"):
+            assert header.get(name) == value, (name, value, header.get(name))
+            checked += 1
+    assert checked >= 18          # 7 modes, 4 reductions, 3 wire types, 4 row orders
+    assert header["REDUCE_PULL"] == 3 and pkg.REDUCE_PULL == 3
